@@ -36,6 +36,7 @@ class KVRequest:
     num_kv_heads: int
     head_dim: int
     window: int = 0          # 0: every key is kept; W > 0: the last W keys
+    shared_values: bool = False   # one tensor serves as keys and values (a cached latent)
 
 
 @dataclass(frozen=True)
@@ -64,7 +65,8 @@ class _KVGroup:
         self.blocks_per_seq = blocks_per_seq
         shape = (len(cache_ids), n_blocks, request.num_kv_heads, block_tokens, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = self.k if request.shared_values else torch.zeros(shape, dtype=dtype,
+                                                                  device=device)
         self.pool = BlockPool(n_blocks)
         self.table_host = np.full((max_slots, blocks_per_seq), -1, dtype=np.int32)
         self.table = torch.full((max_slots, blocks_per_seq), -1, dtype=torch.int32, device=device)
@@ -255,6 +257,19 @@ class SequenceCache:
             for g in self._kv_groups:
                 g.flush()
 
+    # -- state of a step that is run twice ----------------------------------------
+    def has_states(self) -> bool:
+        return bool(self._state)
+
+    def save_states(self, slots: torch.Tensor) -> Dict[int, torch.Tensor]:
+        """Copies of the fixed-size states of ``slots`` (int64 on the device): a step that has
+        to be launched twice (once to warm up, once for good) advances a recurrence once."""
+        return {cid: t.index_select(0, slots) for cid, t in self._state.items()}
+
+    def restore_states(self, slots: torch.Tensor, saved: Dict[int, torch.Tensor]) -> None:
+        for cid, t in self._state.items():
+            t.index_copy_(0, slots, saved[cid])
+
     # -- views -----------------------------------------------------------------
     def kv_view(self, cache_id: int) -> KVView:
         g, i = self._kv_of[cache_id]
@@ -271,7 +286,8 @@ class SequenceCache:
 
     # -- accounting ----------------------------------------------------------------
     def stats(self) -> dict:
-        kv_bytes = sum(g.k.numel() * g.k.element_size() * 2 for g in self._kv_groups)
+        kv_bytes = sum(g.k.numel() * g.k.element_size() * (1 if g.v is g.k else 2)
+                       for g in self._kv_groups)
         state_bytes = sum(t.numel() * t.element_size() for t in self._state.values())
         return {
             "block_tokens": self.block_tokens,

@@ -59,7 +59,8 @@ def main(argv=None) -> int:
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--cache-tokens", type=int, default=None,
-                    help="tokens the cache holds (default: the model's longest sequence)")
+                    help="tokens the cache holds (default: the model's longest sequence, at most "
+                         "32,768)")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                     help="write a model folder with random weights to MODEL first")
@@ -91,7 +92,7 @@ def main(argv=None) -> int:
     t0 = time.time()
     from .config import load_config
     _, cfg, spec = load_config(args.model)
-    cache_tokens = args.cache_tokens or spec.max_positions
+    cache_tokens = args.cache_tokens or min(spec.max_positions, 1 << 15)
     engine = Engine(args.model, dtype=args.dtype, max_tokens=cache_tokens, device=args.device)
     st = engine.stats()
     print(f"model: {spec.architecture}, {len(spec.layers)} layers, hidden {spec.hidden_size}, "

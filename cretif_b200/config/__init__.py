@@ -3,6 +3,7 @@ from .registry import (ConfigError, architecture_name, load_config, read_config_
                        register_architecture, registered_architectures, resolve_architecture)
 from .spec import BranchSpec, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, prenorm_layer
 from .llama import LlamaConfig, build_llama_spec, llama_config_from_dict
+from .rigozen import RigozenConfig, build_rigozen_spec, rigozen_config_from_dict
 from .presets import PRESETS, preset
 
 __all__ = [
@@ -10,4 +11,5 @@ __all__ = [
     "register_architecture", "registered_architectures", "resolve_architecture",
     "BranchSpec", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "prenorm_layer",
     "LlamaConfig", "build_llama_spec", "llama_config_from_dict", "PRESETS", "preset",
+    "RigozenConfig", "build_rigozen_spec", "rigozen_config_from_dict",
 ]

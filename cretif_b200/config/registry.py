@@ -62,10 +62,13 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
 
 def architecture_name(raw: Dict[str, Any]) -> str:
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]            # some configurations name one class, as a string
     if isinstance(archs, str):
         return archs
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json has no 'architectures' list naming the model class")
+        raise ConfigError("config.json has no 'architectures' list (or 'architecture' string) naming "
+                          "the model class")
     return archs[0]
 
 

@@ -34,6 +34,40 @@ int cretif_rope_kv_append(void* qkv, int ld, int dt, const float* cos_t, const f
                           int table_stride, void* kc, void* vc, int bt, int write_cache, int T,
                           unsigned int* fault, void* stream);
 
+// h[r, :] += y[r, :] * weight * rsqrt(mean(y[r]^2) + eps): a norm on a sublayer's output, fused
+// with the residual addition (32-bit).
+int cretif_rmsnorm_add(float* h, const void* y, int y_dt, int ldy, const float* weight, int R,
+                       int H, float eps, void* stream);
+
+// out = h converted to the element type out_dt (the stream handed to a sublayer without a norm).
+int cretif_convert_rows(const float* h, void* out, int out_dt, long long total, void* stream);
+
+// rows [T, ld] = [q (q_dim) | k (nkv * hd) | ...].  With wq: q <- rmsnorm over all q_dim columns
+// times wq, in place.  k: rmsnorm over all nkv*hd columns times wk goes to the key cache at each
+// token's position; with vc, the columns as they are (before the norm) go to the value cache.
+int cretif_proj_norm_kv_append(void* rows, int ld, int dt, int q_dim, const float* wq, int nkv,
+                               int hd, const float* wk, float eps, const int* tok_pos,
+                               const int* tok_seq, const int* seq_slot, const int* table,
+                               int table_stride, void* kc, void* vc, int bt, int write_cache,
+                               int T, unsigned int* fault, void* stream);
+
+// The gated delta rule (delta_rule.cu).  proj rows (float32): [q (G d) | k (G d) | v (H e) |
+// gate (H e) | b (H) | a (H)]; prep rows: [q | k | v | beta (H) | decay (H)].  conv_state and
+// state point at the first sequence slot's saved inputs [C, taps-1] and matrices [H, d, e];
+// state_stride is a slot's size in floats.
+int cretif_delta_prepare(const float* proj, int ldp, float* prep, int ldo, const float* conv_w,
+                         int taps, const float* conv_state, long long state_stride,
+                         const float* a_log, const float* dt_bias, const int* tok_pos,
+                         const int* tok_seq, const int* seq_slot, const int* seq_start, int H,
+                         int G, int d, int e, float unit_eps, int T, void* stream);
+int cretif_delta_conv_state(const float* proj, int ldp, float* conv_state, long long state_stride,
+                            int taps, int C, const int* cu_seqlens, const int* seq_slot, int B,
+                            void* stream);
+int cretif_delta_recurrence(const float* prep, int ldp, const float* gate, int ldg, float* state,
+                            long long state_stride, const int* cu_seqlens, const int* seq_slot,
+                            int B, int H, int G, int d, int e, const float* norm_w, float eps,
+                            void* out, int out_dt, int ldo, int write_state, void* stream);
+
 // After a decode step: ids <- sampled (if given), positions and lengths + 1.
 int cretif_advance_decode(int* tok_ids, int* tok_pos, int* seq_start, const int* sampled, int B,
                           void* stream);
@@ -41,6 +75,12 @@ int cretif_advance_decode(int* tok_ids, int* tok_pos, int* seq_start, const int*
 // C[M,N] (= or +=) A[M,K] · W[N,K]^T, 32-bit FMA on the CUDA cores.
 int cretif_gemm_simt(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt, int M,
                      int N, int K, int lda, int ldw, int ldc, int accumulate, void* stream);
+
+// `batch` products in one launch: product z reads A + z*sa, W + z*sw and writes C + z*sc
+// (strides in elements), e.g. a matrix per head applied to that head's columns of the rows.
+int cretif_gemm_simt_batched(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt,
+                             int M, int N, int K, int lda, int ldw, int ldc, int batch,
+                             long long sa, long long sw, long long sc, void* stream);
 
 // C[M,N] (= or +=) X[M,K] · W[N,K]^T for M <= 64 rows, bfloat16 operands, streaming W once.
 // K and the row strides must be multiples of 8 and the operands 16-byte aligned.
@@ -79,11 +119,12 @@ int cretif_gemm_tc_qkv_rope(const void* A, const void* Wqkv, void* Q, int ldq, c
                             int write_cache, int M, int K, int lda, int ldw, unsigned int* fault,
                             void* stream);
 
-// Causal grouped-query attention over the block cache, any step shape.
+// Causal grouped-query attention over the block cache, any step shape.  sink (may be null):
+// one float per query head, exp(sink) joins the softmax's denominator without a key or value.
 int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int dt, const void* kc,
                      const void* vc, const int* table, int table_stride, const int* tok_pos,
                      const int* tok_seq, const int* seq_slot, int nh, int nkv, int hd, float scale,
-                     int window, int bt, int T, void* stream);
+                     int window, int bt, int T, const float* sink, void* stream);
 
 // Decode attention (one query token per sequence), bfloat16, keys split into n_splits <= 64
 // ranges per (sequence, kv head); part_o/part_ml are float32 scratch of the sizes that

@@ -2,7 +2,7 @@
 //
 // The plain attention kernel: it serves prefill and decode alike, in 32-bit and in
 // bfloat16 storage, for any number of heads and groups, head sizes in steps of 8 up to
-// 256, an optional sliding window, and it is the kernel the faster ones are checked
+// 512, an optional sliding window and an optional per-head sink in the softmax's denominator, and it is the kernel the faster ones are checked
 // against.  Maths as in the reference: s = (q·k)·scale with the scale applied after the
 // dot (src/attention.cu:690-692), keys after the query's position are masked (:60-77),
 // softmax with running maximum and sum in 32-bit as in the reference's decode kernel
@@ -20,7 +20,7 @@
 namespace cretif {
 
 constexpr int kWarps = 8;
-constexpr int kMaxHd = 256;
+constexpr int kMaxHd = 512;
 
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -29,7 +29,7 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
                  const int* __restrict__ table, int table_stride,
                  const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                  const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale,
-                 int window, int bt, int T_tokens) {
+                 int window, int bt, int T_tokens, const float* __restrict__ sink) {
   __shared__ float qs[kMaxHd];
   __shared__ float part_acc[kWarps][kMaxHd];
   __shared__ float part_m[kWarps], part_l[kWarps];
@@ -138,6 +138,15 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
       if (d < hd) acc[i] = fmaf(part_acc[w][d], a, acc[i]);
     }
   }
+  if (sink) {
+    // a sink: one more term exp(sink_h) in the denominator, with no key and no value
+    const float sk = sink[h];
+    const float m2 = fmaxf(m_all, sk);
+    const float a = m_all == -INFINITY ? 0.f : expf(m_all - m2);
+    l_all = l_all * a + expf(sk - m2);
+#pragma unroll
+    for (int i = 0; i < kMaxHd / 32; ++i) acc[i] *= a;
+  }
   const float inv = 1.0f / l_all;
   T* orow = out + (size_t)t * ldo + (size_t)h * hd;
 #pragma unroll
@@ -155,7 +164,7 @@ extern "C" int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int 
                                 const void* vc, const int* table, int table_stride,
                                 const int* tok_pos, const int* tok_seq, const int* seq_slot,
                                 int nh, int nkv, int hd, float scale, int window, int bt, int T,
-                                void* stream) {
+                                const float* sink, void* stream) {
   if (T <= 0) return kOk;
   if (nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hd % 8 || hd > kMaxHd || bt <= 0 ||
       window < 0)
@@ -167,12 +176,12 @@ extern "C" int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int 
   if (dt == kF32)
     attn_simt_kernel<float><<<blocks, kWarps * 32, 0, st>>>(
         (const float*)q, ldq, (float*)out, ldo, (const float*)kc, (const float*)vc, table,
-        table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd, scale, window, bt, T);
+        table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd, scale, window, bt, T, sink);
   else if (dt == kBF16)
     attn_simt_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, st>>>(
         (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, table, table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd,
-        scale, window, bt, T);
+        scale, window, bt, T, sink);
   else
     return kBadDType;
   return launch_status();

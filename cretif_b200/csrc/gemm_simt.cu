@@ -5,6 +5,8 @@
 // operands are K-major, as activations [tokens, in] and weights [out, in] are stored,
 // so nothing is transposed at load (the reference transposes weights on the host for
 // its 32×32 tiled kernel, src/model.cu:141-144, src/kernels/matmul.cu:74-127).
+// cretif_gemm_simt_batched runs `batch` such products in one launch, product z on operands
+// offset by z times an element stride each (per-head matrices on slices of the rows).
 // Any M, N, K; each output sums its products in ascending k whatever M is, so a row's
 // result does not depend on how many other rows are in the call.
 #include "api.h"
@@ -17,7 +19,12 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restrict__ C, int M,
-                 int N, int K, int lda, int ldw, int ldc, int accumulate) {
+                 int N, int K, int lda, int ldw, int ldc, int accumulate, long long sa,
+                 long long sw, long long sc) {
+  // blockIdx.z: one product of a batch (a head's slice of the rows and a matrix of its own)
+  A += (size_t)blockIdx.z * sa;
+  W += (size_t)blockIdx.z * sw;
+  C += (size_t)blockIdx.z * sc;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -84,10 +91,11 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restr
 
 template <typename TA, typename TW, typename TC>
 static int launch(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw,
-                  int ldc, int accumulate, cudaStream_t st) {
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+                  int ldc, int accumulate, cudaStream_t st, int batch = 1, long long sa = 0,
+                  long long sw = 0, long long sc = 0) {
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
   gemm_simt_kernel<TA, TW, TC><<<grid, 256, 0, st>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K,
-                                                     lda, ldw, ldc, accumulate);
+                                                     lda, ldw, ldc, accumulate, sa, sw, sc);
   return launch_status();
 }
 
@@ -111,5 +119,23 @@ extern "C" int cretif_gemm_simt(const void* A, int a_dt, const void* W, int w_dt
     return launch<bf16, bf16, float>(A, W, C, M, N, K, lda, ldw, ldc, accumulate, st);
   if (a_dt == kF32 && w_dt == kBF16 && c_dt == kF32)
     return launch<float, bf16, float>(A, W, C, M, N, K, lda, ldw, ldc, accumulate, st);
+  return kBadDType;
+}
+
+extern "C" int cretif_gemm_simt_batched(const void* A, int a_dt, const void* W, int w_dt, void* C,
+                                        int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
+                                        int batch, long long sa, long long sw, long long sc,
+                                        void* stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return kOk;
+  if (K <= 0 || lda < K || ldw < K || ldc < N || batch > 65535) return kBadArgument;
+  if ((M + BM - 1) / BM > 65535) return kBadArgument;
+  cudaStream_t st = (cudaStream_t)stream;
+  typedef __nv_bfloat16 bf16;
+  if (a_dt == kF32 && w_dt == kF32 && c_dt == kF32)
+    return launch<float, float, float>(A, W, C, M, N, K, lda, ldw, ldc, 0, st, batch, sa, sw, sc);
+  if (a_dt == kBF16 && w_dt == kBF16 && c_dt == kBF16)
+    return launch<bf16, bf16, bf16>(A, W, C, M, N, K, lda, ldw, ldc, 0, st, batch, sa, sw, sc);
+  if (a_dt == kBF16 && w_dt == kBF16 && c_dt == kF32)
+    return launch<bf16, bf16, float>(A, W, C, M, N, K, lda, ldw, ldc, 0, st, batch, sa, sw, sc);
   return kBadDType;
 }

@@ -213,9 +213,120 @@ def gemm_simt(a, w, c, accumulate: bool = False) -> None:
                                   _stream()), "gemm_simt")
 
 
+def gemm_batched(a, w, c) -> None:
+    """c[:, z, :] = a[:, z, :] · w[z]ᵀ for every z: ``a`` [M, Z, K], ``w`` [Z, N, K], ``c``
+    [M, Z, N] (a matrix per head applied to that head's slice of every row), 32-bit FMA."""
+    _need(a, "a", dim=3); _need(w, "w", dim=3); _need(c, "c", dim=3)
+    M, Z, K = a.shape
+    N = w.shape[1]
+    if tuple(w.shape) != (Z, N, K) or tuple(c.shape) != (M, Z, N):
+        raise KernelError(f"gemm_batched: shapes {tuple(a.shape)} x {tuple(w.shape)} -> "
+                          f"{tuple(c.shape)}")
+    if a.stride(2) != 1 or c.stride(2) != 1 or not w.is_contiguous():
+        raise KernelError("gemm_batched: rows must be dense and w contiguous")
+    _check(lib().cretif_gemm_simt_batched(
+        _p(a), _dt(a), _p(w), _dt(w), _p(c), _dt(c), M, N, K, a.stride(0), K, c.stride(0), Z,
+        ctypes.c_longlong(a.stride(1)), ctypes.c_longlong(N * K), ctypes.c_longlong(c.stride(1)),
+        _stream()), "gemm_simt_batched")
+
+
+# ------------------------------------------------------------------ norms beside the sublayers
+def rmsnorm_add(h, y, weight, eps: float) -> None:
+    """h += y * weight * rsqrt(mean(y²) + eps), row by row, in 32-bit."""
+    _need(h, "h", torch.float32, 2); _need(y, "y", dim=2); _need(weight, "weight", torch.float32, 1)
+    R, H = h.shape
+    if tuple(y.shape) != (R, H) or not h.is_contiguous() or weight.numel() != H:
+        raise KernelError("rmsnorm_add: y must match h and weight have H elements")
+    _check(lib().cretif_rmsnorm_add(_p(h), _p(y), _dt(y), _rows(y, "y"), _p(weight), R, H,
+                                    ctypes.c_float(eps), _stream()), "rmsnorm_add")
+
+
+def convert_rows(h, out) -> None:
+    """out = h in out's element type."""
+    _need(h, "h", torch.float32); _need(out, "out")
+    if h.shape != out.shape or not h.is_contiguous() or not out.is_contiguous():
+        raise KernelError("convert_rows: out must match h, both contiguous")
+    _check(lib().cretif_convert_rows(_p(h), _p(out), _dt(out), ctypes.c_longlong(h.numel()),
+                                     _stream()), "convert_rows")
+
+
+def proj_norm_kv_append(rows, q_dim: int, wq, nkv: int, hd: int, wk, eps: float, tok_pos, tok_seq,
+                        seq_slot, table, kc, vc, block_tokens: int, write_cache: bool,
+                        fault) -> None:
+    """``rows`` [T, q_dim + nkv·hd + …]: with ``wq`` the first q_dim columns are RMS-normed as
+    one vector (times wq) in place; the next nkv·hd columns, normed as one vector (times wk), go
+    to the key cache, and as they are to the value cache when ``vc`` is given."""
+    _need(rows, "rows", dim=2); _need(wk, "wk", torch.float32, 1)
+    if wq is not None:
+        _need(wq, "wq", torch.float32, 1)
+        if wq.numel() != q_dim:
+            raise KernelError("proj_norm_kv_append: wq has one weight per query column")
+    if wk.numel() != nkv * hd or rows.shape[1] < q_dim + nkv * hd:
+        raise KernelError("proj_norm_kv_append: sizes do not fit")
+    _need(kc, "k cache", rows.dtype, 4)
+    if tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous():
+        raise KernelError("proj_norm_kv_append: cache must be contiguous "
+                          f"[blocks, {nkv}, {block_tokens}, {hd}]")
+    if vc is not None:
+        _need(vc, "v cache", rows.dtype, 4)
+        if vc.shape != kc.shape or not vc.is_contiguous():
+            raise KernelError("proj_norm_kv_append: the value cache must match the key cache")
+    _check(lib().cretif_proj_norm_kv_append(
+        _p(rows), _rows(rows, "rows"), _dt(rows), q_dim, _p(wq), nkv, hd, _p(wk),
+        ctypes.c_float(eps), _p(tok_pos), _p(tok_seq), _p(seq_slot), _p(table), table.stride(0),
+        _p(kc), _p(vc), block_tokens, int(write_cache), rows.shape[0], _p(fault), _stream()),
+        "proj_norm_kv_append")
+
+
+# ------------------------------------------------------------------ gated delta rule
+def delta_prepare(proj, prep, conv_w, conv_state, a_log, dt_bias, ctx_pos, ctx_seq, seq_slot,
+                  seq_start, H: int, G: int, d: int, e: int, unit_eps: float) -> None:
+    """Convolution over time, SiLU, unit-length q/k, beta and decay of every token.  ``proj``
+    [T, 2Gd + 2He + 2H] and ``prep`` [T, 2Gd + He + 2H] float32; ``conv_state``
+    [slots, …] is the view of the slots' saved inputs ([C, taps-1] each)."""
+    _need(proj, "proj", torch.float32, 2); _need(prep, "prep", torch.float32, 2)
+    _need(conv_w, "conv_w", torch.float32, 2); _need(conv_state, "conv_state", torch.float32, 2)
+    C, taps = conv_w.shape
+    if (C != 2 * G * d + H * e or not conv_w.is_contiguous() or conv_state.stride(1) != 1
+            or conv_state.shape[1] != C * (taps - 1)):
+        raise KernelError("delta_prepare: the convolution's sizes do not fit")
+    _check(lib().cretif_delta_prepare(
+        _p(proj), _rows(proj, "proj"), _p(prep), _rows(prep, "prep"), _p(conv_w), taps,
+        _p(conv_state), ctypes.c_longlong(conv_state.stride(0)), _p(a_log), _p(dt_bias),
+        _p(ctx_pos), _p(ctx_seq), _p(seq_slot), _p(seq_start), H, G, d, e,
+        ctypes.c_float(unit_eps), proj.shape[0], _stream()), "delta_prepare")
+
+
+def delta_conv_state(proj, conv_state, taps: int, C: int, cu_seqlens, seq_slot, B: int) -> None:
+    """Save every sequence's last taps-1 inputs of the C convolved channels."""
+    _need(proj, "proj", torch.float32, 2); _need(conv_state, "conv_state", torch.float32, 2)
+    _check(lib().cretif_delta_conv_state(
+        _p(proj), _rows(proj, "proj"), _p(conv_state), ctypes.c_longlong(conv_state.stride(0)),
+        taps, C, _p(cu_seqlens), _p(seq_slot), B, _stream()), "delta_conv_state")
+
+
+def delta_recurrence(prep, gate, state, cu_seqlens, seq_slot, B: int, H: int, G: int, d: int,
+                     e: int, norm_w, eps: float, out, write_state: bool = True) -> None:
+    """The recurrence over the step's tokens of every (sequence, head), from and to ``state``
+    (view [slots, H·d·e] float32), then the per-head RMS norm times ``norm_w`` times
+    SiLU(``gate``) → ``out`` [T, H·e]."""
+    _need(prep, "prep", torch.float32, 2); _need(gate, "gate", torch.float32, 2)
+    _need(state, "state", torch.float32, 2); _need(out, "out", dim=2)
+    _need(norm_w, "norm_w", torch.float32, 1)
+    if state.stride(1) != 1 or state.shape[1] != H * d * e or norm_w.numel() != e:
+        raise KernelError("delta_recurrence: the state's sizes do not fit")
+    _check(lib().cretif_delta_recurrence(
+        _p(prep), _rows(prep, "prep"), _p(gate), _rows(gate, "gate"), _p(state),
+        ctypes.c_longlong(state.stride(0)), _p(cu_seqlens), _p(seq_slot), B, H, G, d, e,
+        _p(norm_w), ctypes.c_float(eps), _p(out), _dt(out), _rows(out, "out"), int(write_state),
+        _stream()), "delta_recurrence")
+
+
 # ------------------------------------------------------------------ attention
 def attn_simt(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
-              scale: float, window: int, block_tokens: int) -> None:
+              scale: float, window: int, block_tokens: int, sink=None) -> None:
+    """``sink`` (float32 [heads], optional): exp(sink_h) joins head h's softmax denominator
+    without a key or a value."""
     _need(q, "q", dim=2); _need(out, "out", q.dtype, 2)
     _need(kc, "k cache", q.dtype, 4); _need(vc, "v cache", q.dtype, 4)
     T = q.shape[0]
@@ -224,12 +335,16 @@ def attn_simt(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: i
     if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
             or not vc.is_contiguous()):
         raise KernelError("attention: cache must be contiguous [blocks, kv_heads, block, head_dim]")
-    if hd % 8 or hd > 256:
-        raise KernelError(f"attention: head_dim {hd} is not a multiple of 8 up to 256")
+    if hd % 8 or hd > 512:
+        raise KernelError(f"attention: head_dim {hd} is not a multiple of 8 up to 512")
+    if sink is not None:
+        _need(sink, "sink", torch.float32, 1)
+        if sink.numel() != nh or not sink.is_contiguous():
+            raise KernelError("attention: the sink has one number per query head")
     _check(lib().cretif_attn_simt(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _dt(q), _p(kc), _p(vc), _p(table),
         table.stride(0), _p(tok_pos), _p(tok_seq), _p(seq_slot), nh, nkv, hd,
-        ctypes.c_float(scale), window, block_tokens, T, _stream()), "attn_simt")
+        ctypes.c_float(scale), window, block_tokens, T, _p(sink), _stream()), "attn_simt")
 
 
 # ------------------------------------------------------------------ sampling

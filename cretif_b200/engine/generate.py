@@ -196,9 +196,16 @@ class DecodeRunner:
             saved = b["ints"].clone()
             cur = torch.cuda.current_stream()
             self.stream.wait_stream(cur)
+            cache = self.engine.cache
             with torch.cuda.stream(self.stream):
+                # keys and values are written to the same place twice; a recurrent state
+                # would advance twice, so it is put back after the warm-up
+                slots = b["seq_slot"].to(torch.int64) if cache.has_states() else None
+                states = cache.save_states(slots) if slots is not None else None
                 self._body(b, B, context)
                 b["ints"].copy_(saved)
+                if states is not None:
+                    cache.restore_states(slots, states)
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, pool=self.pool, stream=self.stream):
                     self._body(b, B, context)

@@ -7,6 +7,12 @@ scaled after the dot product, causal mask, softmax, weighted sum of values
 (:683-714), output projection (:720-728).  Unlike the reference there is no separate
 score tensor and no transposition of the cache: the attention kernels read the
 cache's blocks directly, for whole prompts and for single tokens alike.
+
+Two options change what is projected and normed: ``qk_norm`` applies an RMS norm with a
+weight per channel over the WHOLE query projection and over the whole key projection (all
+heads of a token as one vector) before the heads are split; ``values: "keys"`` drops the value
+projection, the values being the keys as projected, before that norm.  ``sink`` names a tensor
+with one number per query head whose exponential joins the softmax's denominator.
 """
 from __future__ import annotations
 
@@ -43,11 +49,35 @@ def force_plain_attention(on: bool) -> None:
     _force_plain = bool(on)
 
 
+def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None):
+    """Causal (windowed) attention of the step's queries ``q`` [T, nh·hd] over the cache view
+    ``kv`` into ``o``, with the kernel that fits the step: the decode kernels when every
+    sequence brings one token, the prompt kernel otherwise, the plain kernel for float32 and
+    for whatever the fast ones do not take."""
+    if not _force_plain and dtype == torch.bfloat16 and sink is None:
+        if ctx.is_decode and ops.attn_decode_supported(hd, kv.block_tokens, nh // nkv):
+            splits, cluster = ops.decode_plan(ctx.B, nkv, ctx.max_context, q.device, hd)
+            ops.attn_decode(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq,
+                            ctx.seq_slot, nh, nkv, hd, scale, window, kv.block_tokens, splits,
+                            ctx.fault, cluster)
+            return
+        if not ctx.is_decode and ops.attn_prefill_supported(hd, kv.block_tokens):
+            ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx.cu_seqlens, ctx.seq_start,
+                             ctx.seq_slot, nh, nkv, hd, scale, window, kv.block_tokens, ctx.B,
+                             ctx.max_new, ctx.fault)
+            return
+    ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
+                  nh, nkv, hd, scale, window, kv.block_tokens, sink=sink)
+
+
 @register_part("mixer", "attention")
 class Attention(Part):
     """params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``scale``, ``window``
     (0 = all keys), ``position`` (a position part's kind and constants), ``names``
-    (tensor names of q, k, v, o relative to the layer's prefix)."""
+    (tensor names of q, k, v, o relative to the layer's prefix).  Optional: ``qk_norm``
+    (``{"eps", "q": name, "k": name}``: RMS norm over the whole q and k projections),
+    ``values`` (``"keys"``: no value projection, the un-normed keys are the values; needs
+    ``qk_norm`` or no position encoding), ``sink`` (name of a [heads] tensor)."""
 
     graph_safe = True
 
@@ -60,28 +90,54 @@ class Attention(Part):
         self.window = int(params.get("window", 0))
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
             raise ValueError(f"attention: {self.nh} heads cannot share {self.nkv} key/value heads")
-        if self.hd % 16 or not 16 <= self.hd <= 256:
-            raise ValueError(f"attention: head_dim {self.hd} is not a multiple of 16 in [16, 256]; "
+        if self.hd % 8 or not 8 <= self.hd <= 512:
+            raise ValueError(f"attention: head_dim {self.hd} is not a multiple of 8 in [8, 512]; "
                              "the attention kernels take no other head size")
         pos = dict(params.get("position") or {"kind": "none"})
         self.position = build_part("position", PartSpec(pos.pop("kind"), pos), hidden_size,
                                    dtype, device)
         self.q_dim, self.kv_dim = self.nh * self.hd, self.nkv * self.hd
+        self.qk_norm = params.get("qk_norm")
+        self.values_are_keys = params.get("values", "projected") == "keys"
+        if params.get("values", "projected") not in ("projected", "keys"):
+            raise ValueError(f"attention: values must be 'projected' or 'keys', got "
+                             f"{params['values']!r}")
+        if self.values_are_keys and self.qk_norm is None:
+            raise ValueError("attention: values taken from the keys need qk_norm (the kernel "
+                             "that norms the keys stores both)")
+        if self.qk_norm is not None and (params.get("position") or {}).get("kind", "none") != "none":
+            raise ValueError("attention: qk_norm over the whole projection is built without a "
+                             "position encoding only")
+        self.sink = None
 
     @classmethod
     def weight_specs(cls, params, hidden_size):
         q = params["num_heads"] * params["head_dim"]
         kv = params["num_kv_heads"] * params["head_dim"]
         n = params["names"]
-        return {"q": (n["q"], WeightSpec((q, hidden_size))),
-                "k": (n["k"], WeightSpec((kv, hidden_size))),
-                "v": (n["v"], WeightSpec((kv, hidden_size))),
-                "o": (n["o"], WeightSpec((hidden_size, q)))}
+        out = {"q": (n["q"], WeightSpec((q, hidden_size))),
+               "k": (n["k"], WeightSpec((kv, hidden_size))),
+               "o": (n["o"], WeightSpec((hidden_size, q)))}
+        if params.get("values", "projected") != "keys":
+            out["v"] = (n["v"], WeightSpec((kv, hidden_size)))
+        if params.get("qk_norm"):
+            out["q_norm"] = (params["qk_norm"]["q"], WeightSpec((q,), init=(1.0, 0.1)))
+            out["k_norm"] = (params["qk_norm"]["k"], WeightSpec((kv,), init=(1.0, 0.1)))
+        if params.get("sink"):
+            out["sink"] = (params["sink"], WeightSpec((params["num_heads"],), init=(0.0, 1.0)))
+        return out
 
     def load(self, tensors):
         # one product for q, k and v: rows [q | k | v] of the stacked matrix
-        self.w_qkv = self._matrix(torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0))
+        stacked = [tensors["q"], tensors["k"]] + ([] if self.values_are_keys else [tensors["v"]])
+        self.w_qkv = self._matrix(torch.cat(stacked, dim=0))
         self.w_o = self._matrix(tensors["o"])
+        if self.qk_norm is not None:
+            self.q_norm_w = self._vector32(tensors["q_norm"])
+            self.k_norm_w = self._vector32(tensors["k_norm"])
+            self.qk_eps = float(self.qk_norm["eps"])
+        if "sink" in tensors:
+            self.sink = self._vector32(tensors["sink"])
         self.position.load({})
 
     def prepare(self, max_positions: int) -> None:
@@ -99,7 +155,21 @@ class Attention(Part):
         rot = getattr(self.position, "rotary_table", None)
         rot = rot() if rot is not None else None         # (cos, sin, pairing, rotary_dim)
         o = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
-        if (self.dtype == torch.bfloat16 and ctx.T > skinny_max_rows() and not plain_forced()
+        if self.qk_norm is not None:
+            # norms over the whole projections; the kernel that norms the keys stores them
+            # (and, when the values are the keys, the un-normed columns as values)
+            qkv = linear(x, self.w_qkv)
+            if not self.values_are_keys and cache.writes:
+                ops.rope_kv_append(qkv, None, None, 0, 0, self.nh, self.nkv, self.hd,
+                                   ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.table, kv.k,
+                                   kv.v, kv.block_tokens, True, ctx.fault)
+            ops.proj_norm_kv_append(qkv, self.q_dim, self.q_norm_w, self.nkv, self.hd,
+                                    self.k_norm_w, self.qk_eps, ctx.tok_pos, ctx.tok_seq,
+                                    ctx.seq_slot, kv.table, kv.k,
+                                    kv.v if self.values_are_keys else None, kv.block_tokens,
+                                    cache.writes, ctx.fault)
+            self.attend(qkv, o, ctx, kv)
+        elif (self.dtype == torch.bfloat16 and ctx.T > skinny_max_rows() and not plain_forced()
                 and not _force_plain and self.hd in (64, 128) and rot is not None
                 and rot[3] == self.hd and ops.gemm_tc_supported(x, self.w_qkv, o)):
             # many tokens: rotary and the cache write ride in the product's epilogue
@@ -130,6 +200,8 @@ class Attention(Part):
         """bfloat16.  Few tokens: norm + q|k|v + rotary + cache write in one kernel, attention,
         then the output projection added into ``h``.  Many tokens: the same through the norm's
         kernel and the tensor-core products.  False if the step does not qualify."""
+        if norm is None:
+            return False
         if (ctx.T > FUSED_MAX_TOKENS and self.dtype == torch.bfloat16 and not _force_plain
                 and h.dtype == torch.float32 and h.is_contiguous()):
             # many tokens: the norm's own kernel, then the products; the last one adds its
@@ -140,6 +212,7 @@ class Attention(Part):
         rms = getattr(norm, "rms_params", None)
         rot = getattr(self.position, "rotary_table", None)
         if (_force_plain or not fused_steps_enabled() or self.dtype != torch.bfloat16
+                or self.qk_norm is not None or self.sink is not None
                 or ctx.T > FUSED_MAX_TOKENS or rms is None or rot is None or cache is None
                 or cache.kv is None or cache.kv.block_tokens & (cache.kv.block_tokens - 1)
                 or not ops.fused_supported(ctx.T, self.hidden_size, self.w_qkv)
@@ -160,22 +233,8 @@ class Attention(Part):
         return True
 
     def attend(self, q, o, ctx, kv):
-        if not _force_plain and self.dtype == torch.bfloat16:
-            if ctx.is_decode and ops.attn_decode_supported(self.hd, kv.block_tokens,
-                                                           self.nh // self.nkv):
-                splits, cluster = ops.decode_plan(ctx.B, self.nkv, ctx.max_context, q.device,
-                                                  self.hd)
-                ops.attn_decode(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq,
-                                ctx.seq_slot, self.nh, self.nkv, self.hd, self.scale,
-                                self.window, kv.block_tokens, splits, ctx.fault, cluster)
-                return
-            if not ctx.is_decode and ops.attn_prefill_supported(self.hd, kv.block_tokens):
-                ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx.cu_seqlens, ctx.seq_start,
-                                 ctx.seq_slot, self.nh, self.nkv, self.hd, self.scale,
-                                 self.window, kv.block_tokens, ctx.B, ctx.max_new, ctx.fault)
-                return
-        ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
-                      self.nh, self.nkv, self.hd, self.scale, self.window, kv.block_tokens)
+        run_attention(q, o, ctx, kv, self.nh, self.nkv, self.hd, self.scale, self.window,
+                      self.dtype, self.sink)
 
     def weight_bytes(self):
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()

@@ -9,7 +9,10 @@ ordered list of the layer's branches (role, part, norm before it, norm after it)
 ``caches[k]`` is what branch ``k`` keeps between steps (or ``None``).
 
 ``residual``: one branch after the other, ``h += post_norm(part(norm(h)))`` each.  With a
-mixer and a feed-forward behind a norm each this is the reference's block.
+mixer and a feed-forward behind a norm each this is the reference's block.  A branch without
+a norm hands its part the stream itself (converted to the part's compute type); a norm after
+the part that offers ``add_into(h, y)`` norms the part's output and adds it to the stream in
+one 32-bit kernel.
 
 A part may offer ``forward_from_residual(h, norm, ctx[, cache]) -> bool``: it then reads
 the residual stream itself, applies the given norm inside its first kernel and adds its
@@ -19,7 +22,19 @@ and the returned branch.  Parts without the method just use that path.
 """
 from __future__ import annotations
 
+import torch
+
+from ..csrc import ops
 from .base import register_part
+
+
+def stream_as(h, dtype):
+    """The 32-bit residual stream in a part's compute type (itself when that is float32)."""
+    if dtype == h.dtype:
+        return h
+    x = torch.empty(h.shape, dtype=dtype, device=h.device)
+    ops.convert_rows(h, x)
+    return x
 
 
 def call_part(branch, x, ctx, cache):
@@ -46,9 +61,12 @@ def run_residual(layer, h, pending, ctx, caches):
             if pending is not None:
                 h.add_(pending)
                 pending = None
-            x = h.to(part.dtype)
+            x = stream_as(h, part.dtype)                     # the part reads the stream itself
         y = call_part(branch, x, ctx, cache)
         if branch.post_norm is not None:
+            if hasattr(branch.post_norm, "add_into"):
+                branch.post_norm.add_into(h, y)              # h += norm(y), 32-bit, one kernel
+                continue
             y = branch.post_norm.forward(y.to(h.dtype).contiguous())
         pending = y
     return pending

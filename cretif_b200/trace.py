@@ -68,12 +68,18 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder the <step>.f32 files are written to")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
     from .engine import Engine
-    engine = Engine(args.model, dtype=args.dtype, max_tokens=args.max_tokens, device=args.device)
+    # --max-tokens counts the tokens themselves; the cache hands out whole blocks, so every
+    # live request may leave part of its last block unused.  Room for that is added for as
+    # many requests as can be live at once (each holds a token at least), up to 256.
+    block = 64
+    slack = block * min(max(args.max_tokens, 1), 256)
+    engine = Engine(args.model, dtype=args.dtype, max_tokens=args.max_tokens + slack,
+                    device=args.device, block_tokens=block, max_len=args.max_tokens)
 
     def report(text):
         sys.stdout.write(text + "\n")
