@@ -149,6 +149,16 @@ int cretif_attn_decode_mma(const void* q, int ldq, void* out, int ldo, const voi
                            float* part_o, float* part_ml, int* counters, unsigned int* fault,
                            void* stream);
 
+// The same with a sink (may be null): one float per query head whose exponential joins the
+// softmax's denominator where the ranges are merged.
+int cretif_attn_decode_mma_sink(const void* q, int ldq, void* out, int ldo, const void* kc,
+                                const void* vc, long long n_blocks, const int* table,
+                                int table_stride, const int* tok_pos, const int* tok_seq,
+                                const int* seq_slot, int nh, int nkv, int hd, float scale,
+                                int window, int bt, int B, int n_splits, float* part_o,
+                                float* part_ml, int* counters, const float* sink,
+                                unsigned int* fault, void* stream);
+
 // Fused decode projections (see decode_fused.cu).  H is the float32 residual stream; when it
 // is given, x = bf16(rmsnorm(H[rows])) is computed in the kernel, else X (bfloat16) is read.
 int cretif_fused_linear(const void* X, int ldx, const float* H, const float* norm_w,
@@ -187,6 +197,15 @@ int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out, int ldo, 
                            const int* cu_seqlens, const int* seq_start, const int* seq_slot,
                            int nh, int nkv, int hd, float scale, int window, int bt, int B,
                            int max_new, unsigned int* fault, void* stream);
+
+// The same with a sink (may be null): one float per query head whose exponential joins each
+// row's denominator (the kernel with two threads per row serves it).
+int cretif_attn_prefill_tc_sink(const void* qkv, int ldq, int T, void* out, int ldo,
+                                const void* kc, const void* vc, long long n_blocks,
+                                const int* table, int table_stride, const int* cu_seqlens,
+                                const int* seq_start, const int* seq_slot, int nh, int nkv, int hd,
+                                float scale, int window, int bt, int B, int max_new,
+                                const float* sink, unsigned int* fault, void* stream);
 
 // One CTA waits, with the library's bounded wait, on a barrier that nothing completes; after
 // `limit` polls (at most 2^20) it gives up, sets bit 2 of *fault and returns.  *polls (may be

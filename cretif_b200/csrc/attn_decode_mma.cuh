@@ -101,7 +101,9 @@ __device__ __forceinline__ void attn_decode_mma_item(
     float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
     int ldo, int* __restrict__ counters, unsigned int* __restrict__ fault, int split,
     int n_splits, int kvh, int b, uint32_t& it_base, unsigned long long* stamps = nullptr,
-    int n_stages = kDmStages) {
+    int n_stages = kDmStages, const float* __restrict__ sink = nullptr) {
+  // sink (may be null): one number per query head; exp(sink) joins the denominator of that
+  // head's softmax where the ranges are merged, with no key and no value.
   constexpr int hd = HD16 * 16;
   // Tuning aid: with a buffer given, lane 0 of every warp of the first CTA notes the time at
   // which it passes each phase ([warp][16]); the CTA that merges notes its own at [8][..].
@@ -383,6 +385,7 @@ __device__ __forceinline__ void attn_decode_mma_item(
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       ll += __shfl_xor_sync(0xffffffffu, ll, 1);
       ll += __shfl_xor_sync(0xffffffffu, ll, 2);
+      if (sink && live) ll += exp2f(sink[kvh * g + j] * 1.4426950408889634f - mm);
       if (live && w == 0)
         out[(size_t)b * ldo + (size_t)kvh * g * hd + i] = __float2bfloat16_rn(acc / ll);
     }
@@ -444,7 +447,10 @@ __device__ __forceinline__ void attn_decode_mma_item(
       den += w * ls;
     }
     den = warp_sum(den);
-    if (lane == 0) inv_den[j] = 1.0f / den;
+    if (lane == 0) {
+      if (sink) den += exp2f(sink[kvh * g + j] * 1.4426950408889634f - mx);
+      inv_den[j] = 1.0f / den;
+    }
   }
   __syncthreads();
   if (stamping_last && threadIdx.x == 0) stamp(8, 1);
@@ -508,7 +514,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
                        int window, float* __restrict__ part_o, float* __restrict__ part_ml,
                        __nv_bfloat16* __restrict__ out, int ldo, int* __restrict__ counters,
                        unsigned int* __restrict__ fault, unsigned long long* stamps,
-                       int n_stages) {
+                       int n_stages, const float* __restrict__ sink) {
   extern __shared__ unsigned char smem_raw[];
   if (kStamps && stamps && blockIdx.x + blockIdx.y + blockIdx.z == 0 && threadIdx.x == 0) {
     unsigned long long t;
@@ -524,7 +530,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
   attn_decode_mma_item<HD16, CLUSTER>(smem, &map_k, &map_v, q, ldq, table, table_stride, tok_pos,
                                       tok_seq, seq_slot, nh, nkv, scale_log2, window, part_o,
                                       part_ml, out, ldo, counters, fault, blockIdx.x, gridDim.x,
-                                      blockIdx.y, blockIdx.z, it_base, stamps, n_stages);
+                                      blockIdx.y, blockIdx.z, it_base, stamps, n_stages, sink);
 }
 
 }  // namespace cretif

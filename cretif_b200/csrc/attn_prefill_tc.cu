@@ -96,7 +96,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                        const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale_log2,
                        int window, unsigned int* __restrict__ fault,
-                       unsigned long long* stamps) {
+                       unsigned long long* stamps, const float* __restrict__ sink) {
   extern __shared__ unsigned char smem_raw[];
   // Tuning aid: with a buffer given, the first CTA (the heaviest tile) notes the times at
   // which its MMA thread and one softmax thread pass the phases of steps 0 .. 7:
@@ -388,6 +388,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     xb[half * 128 + row] = l;
     asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
     l += xb[(half ^ 1) * 128 + row];
+    // a sink: exp(sink_h) joins the row's denominator, with no key and no value (both halves
+    // of a row hold the same reference m)
+    if (sink) l += exp2f(sink[h] * 1.4426950408889634f - m);
     if (ok && row_valid) {
       const float inv = 1.0f / l;
       __nv_bfloat16* orow = out + (size_t)(tok0 + q0 + row) * ldo + (size_t)h * hd + obase;
@@ -848,6 +851,19 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
                                       const int* seq_start, const int* seq_slot, int nh, int nkv,
                                       int hd, float scale, int window, int bt, int B, int max_new,
                                       unsigned int* fault, void* stream) {
+  return cretif_attn_prefill_tc_sink(qkv, ldq, T, out, ldo, kc, vc, n_blocks, table, table_stride,
+                                     cu_seqlens, seq_start, seq_slot, nh, nkv, hd, scale, window,
+                                     bt, B, max_new, nullptr, fault, stream);
+}
+
+extern "C" int cretif_attn_prefill_tc_sink(const void* qkv, int ldq, int T, void* out, int ldo,
+                                           const void* kc, const void* vc, long long n_blocks,
+                                           const int* table, int table_stride,
+                                           const int* cu_seqlens, const int* seq_start,
+                                           const int* seq_slot, int nh, int nkv, int hd,
+                                           float scale, int window, int bt, int B, int max_new,
+                                           const float* sink, unsigned int* fault,
+                                           void* stream) {
   if (B <= 0 || T <= 0) return kOk;
   if (nh <= 0 || nkv <= 0 || nh % nkv || hd % 16 || hd < 16 || hd > 128 || bt != kPfBlk ||
       window < 0 || !(scale > 0.f) || max_new <= 0 || B > 65535 || ldq % 8 || ldo % 8 ||
@@ -888,7 +904,7 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const bool rows_ok = g_pf_pairing != 0 && hd <= 64 && window == 0 && items <= 65535;
+  const bool rows_ok = g_pf_pairing != 0 && hd <= 64 && window == 0 && items <= 65535 && !sink;
   const bool paired = rows_ok && (g_pf_pairing == 1 ||
                                   (g_pf_pairing < 0 && 5 * pairs * nkv * B >= 7LL * sm_count));
   if (rows_ok) {
@@ -920,7 +936,7 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
     }
     e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel<64>, map_q, map_k, map_v,
                            (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
-                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps);
+                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps, sink);
     if (e != cudaSuccess) return (int)e;
   } else {
     static int configured = 0;
@@ -932,7 +948,7 @@ extern "C" int cretif_attn_prefill_tc(const void* qkv, int ldq, int T, void* out
     }
     e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel<128>, map_q, map_k, map_v,
                            (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
-                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps);
+                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps, sink);
     if (e != cudaSuccess) return (int)e;
   }
   return launch_status();

@@ -509,7 +509,13 @@ def decode_plan(B: int, nkv: int, max_context: int, device, hd: int = 64):
 
 def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
                 scale: float, window: int, block_tokens: int, n_splits: int, fault,
-                cluster: bool = False) -> None:
+                cluster: bool = False, sink=None) -> None:
+    """``sink`` (float32 [heads], optional; tensor-core kernel only): exp(sink_h) joins head h's
+    softmax denominator."""
+    if sink is not None:
+        _need(sink, "sink", torch.float32, 1)
+        if sink.numel() != nh or hd > 128 or _decode_simt_only:
+            raise KernelError("attn_decode: a sink needs one number per head and head_dim <= 128")
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
     _need(kc, "k cache", torch.bfloat16, 4); _need(vc, "v cache", torch.bfloat16, 4)
     B = q.shape[0]
@@ -522,21 +528,22 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
         if hd > 128 or _decode_simt_only or n_splits > CLUSTER_MAX_RANGES:
             raise KernelError("attn_decode: the cluster merge takes head sizes up to 128 and at "
                               f"most {CLUSTER_MAX_RANGES} ranges")
-        _check(lib().cretif_attn_decode_mma(
+        _check(lib().cretif_attn_decode_mma_sink(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc),
             ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
             _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
-            None, None, None, _p(fault), _stream()), "attn_decode_mma")
+            None, None, None, _p(sink), _p(fault), _stream()), "attn_decode_mma")
         return
     part_o = torch.empty((B, nh, n_splits, hd), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((B, nh, n_splits, 2), dtype=torch.float32, device=q.device)
     counters = _decode_counters(q.device, B * nkv)
     if hd <= 128 and not _decode_simt_only:
-        _check(lib().cretif_attn_decode_mma(
+        _check(lib().cretif_attn_decode_mma_sink(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc),
             ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
             _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
-            _p(part_o), _p(part_ml), _p(counters), _p(fault), _stream()), "attn_decode_mma")
+            _p(part_o), _p(part_ml), _p(counters), _p(sink), _p(fault), _stream()),
+            "attn_decode_mma")
         return
     _check(lib().cretif_attn_decode(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc), _p(table),
@@ -728,15 +735,20 @@ def attn_prefill_supported(hd: int, block_tokens: int) -> bool:
 
 def attn_prefill(qkv, out, kc, vc, table, cu_seqlens, seq_start, seq_slot, nh: int, nkv: int,
                  hd: int, scale: float, window: int, block_tokens: int, B: int, max_new: int,
-                 fault) -> None:
-    """Causal attention of whole prompts; ``qkv`` rows start with the query heads."""
+                 fault, sink=None) -> None:
+    """Causal attention of whole prompts; ``qkv`` rows start with the query heads.  ``sink``
+    (float32 [heads], optional): exp(sink_h) joins head h's softmax denominator."""
+    if sink is not None:
+        _need(sink, "sink", torch.float32, 1)
+        if sink.numel() != nh:
+            raise KernelError("attn_prefill: the sink has one number per query head")
     _need(qkv, "qkv", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2)
     _need(kc, "k cache", torch.bfloat16, 4); _need(vc, "v cache", torch.bfloat16, 4)
     if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
             or not vc.is_contiguous()):
         raise KernelError("attn_prefill: cache must be contiguous [blocks, kv_heads, 64, head_dim]")
-    _check(lib().cretif_attn_prefill_tc(
+    _check(lib().cretif_attn_prefill_tc_sink(
         _p(qkv), _rows(qkv, "qkv"), qkv.shape[0], _p(out), _rows(out, "out"), _p(kc), _p(vc),
         ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(cu_seqlens), _p(seq_start),
         _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, max_new,
-        _p(fault), _stream()), "attn_prefill_tc")
+        _p(sink), _p(fault), _stream()), "attn_prefill_tc")

@@ -54,17 +54,24 @@ def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None):
     ``kv`` into ``o``, with the kernel that fits the step: the decode kernels when every
     sequence brings one token, the prompt kernel otherwise, the plain kernel for float32 and
     for whatever the fast ones do not take."""
-    if not _force_plain and dtype == torch.bfloat16 and sink is None:
-        if ctx.is_decode and ops.attn_decode_supported(hd, kv.block_tokens, nh // nkv):
-            splits, cluster = ops.decode_plan(ctx.B, nkv, ctx.max_context, q.device, hd)
-            ops.attn_decode(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq,
-                            ctx.seq_slot, nh, nkv, hd, scale, window, kv.block_tokens, splits,
-                            ctx.fault, cluster)
+    if not _force_plain and dtype == torch.bfloat16 and (sink is None or hd <= 128):
+        if ctx.is_decode and ops.attn_decode_supported(hd, kv.block_tokens, min(nh // nkv, 8)) \
+                and (nh // nkv <= 8 or nkv == 1):
+            # the kernel takes up to eight query heads per key/value head; more heads on ONE
+            # key/value head (a shared latent) go eight at a time
+            step = nh if nh // nkv <= 8 else 8
+            for h0 in range(0, nh, step):
+                n = min(step, nh - h0)
+                splits, cluster = ops.decode_plan(ctx.B, nkv, ctx.max_context, q.device, hd)
+                ops.attn_decode(q[:, h0 * hd:], o[:, h0 * hd:], kv.k, kv.v, kv.table,
+                                ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, n, nkv, hd, scale,
+                                window, kv.block_tokens, splits, ctx.fault, cluster,
+                                sink=None if sink is None else sink[h0:h0 + n])
             return
         if not ctx.is_decode and ops.attn_prefill_supported(hd, kv.block_tokens):
             ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx.cu_seqlens, ctx.seq_start,
                              ctx.seq_slot, nh, nkv, hd, scale, window, kv.block_tokens, ctx.B,
-                             ctx.max_new, ctx.fault)
+                             ctx.max_new, ctx.fault, sink=sink)
             return
     ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
                   nh, nkv, hd, scale, window, kv.block_tokens, sink=sink)
