@@ -20,6 +20,14 @@ fraction for each); ``prefill_b8`` and ``prefill_b64`` are steps over 8 and 64 p
 ``--size 360m --unequal`` decodes after prompts of unequal lengths 256..2,048;
 ``--dtype float32`` measures the true 32-bit path.
 Every weight plus the cache exceed the L2 cache, so no flush is needed between steps.
+
+    python bench.py --design rigozen [--design-size s|m] [--layers L]
+
+measures another thing and leaves the line above as it is: prefill (1 and 8 prompts of 2,048
+tokens) and decode (batch 1, 8, 64 from a context of 2,048) of Rigozen models whose layers
+have real sizes -- all layers of one mixer (attention with keys as values, latent attention,
+gated delta rule) and a mixture -- beside the Llama model of the same width, feed-forward,
+heads and window, each with a roofline fraction (see design_bench).
 """
 from __future__ import annotations
 
@@ -297,6 +305,113 @@ def run_e2e(engine, batch, steps, prompt_len):
     return out
 
 
+# Layer sizes for --design: width, feed-forward, vocabulary; heads / key-value heads / head size
+# of the attention layers and of the Llama model beside them; the latent's rank; the delta
+# rule's heads and sizes; the window of every attention layer (Llama's too).
+DESIGN_SIZES = {
+    "s": dict(width=576, ff=1536, vocab=49152, heads=9, kv=3, dim=64, rank=128,
+              d_heads=9, d_dim=64, d_vdim=64, window=1024),
+    "m": dict(width=2048, ff=8192, vocab=49152, heads=32, kv=8, dim=64, rank=128,
+              d_heads=16, d_dim=128, d_vdim=128, window=1024),
+}
+
+
+def design_configs(z, layers):
+    """name -> config.json of the models --design measures."""
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
+           "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}}
+    lat = {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "kv_rank": z["rank"],
+           "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}}
+    dlt = {"heads": z["d_heads"], "kv_heads": z["d_heads"], "dim": z["d_dim"],
+           "vdim": z["d_vdim"], "conv": 4}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    kinds = {"attention": att, "latent_attention": lat, "delta": dlt}
+
+    def rigozen(order):
+        return {"architecture": "Rigozen", "vocab": z["vocab"], "width": z["width"],
+                "norm": {"eps": 1e-6}, "max_positions": CONTEXT,
+                "layers": [{"type": k, "mixer": kinds[k], "mlp": mlp} for k in order]}
+    mixed = (["attention", "delta", "delta", "latent_attention"] * layers)[:layers]
+    out = {"llama": {"architectures": ["LlamaForCausalLM"], "hidden_size": z["width"],
+                     "num_hidden_layers": layers, "num_attention_heads": z["heads"],
+                     "num_key_value_heads": z["kv"], "head_dim": z["dim"],
+                     "intermediate_size": z["ff"], "vocab_size": z["vocab"],
+                     "rope_theta": 100000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+                     "max_position_embeddings": CONTEXT, "sliding_window": z["window"]}}
+    for k in kinds:
+        out["rigozen " + k] = rigozen([k] * layers)
+    out["rigozen mixed"] = rigozen(mixed)
+    return out
+
+
+def design_bench(args) -> int:
+    """Rigozen at real layer sizes beside Llama at the same sizes; one JSON line.
+
+    Roofline of a prefill step: the FLOPs of its matrix products (every weight but the
+    embedding table, twice per token, the head on the last rows only) and of the windowed
+    attention, over the measured bf16 peak.  Of a decode step: every weight once plus what the
+    live requests keep (keys/values or latents inside the window, the delta rule's matrices read
+    and written) over the measured copy bandwidth.  The delta rule's recurrence is counted as
+    what it has to do (4 d e multiply-adds a token and head), not as what a tensor-core
+    formulation would add."""
+    import torch
+    from cretif_b200.engine import Engine
+    from cretif_b200.weights.random_model import write_random_model
+    z = DESIGN_SIZES[args.design_size]
+    layers = args.layers or 8
+    pk = peaks()
+    T, W, V = PROMPT_LEN, z["width"], z["vocab"]
+    rows = {}
+    with ClockSampler() as clocks:
+        for name, cfg in design_configs(z, layers).items():
+            tmp = tempfile.mkdtemp(prefix="cretif_design_")
+            try:
+                write_random_model(tmp, cfg, seed=99)
+                engine = Engine(tmp, dtype=args.dtype, max_tokens=64 * CONTEXT + 64 * 64,
+                                max_len=CONTEXT, max_slots=80)
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            wbytes = engine.model.weight_bytes()
+            params = wbytes / (2 if args.dtype == "bfloat16" else 4)
+            window = z["window"]
+            kinds = ([l["type"] for l in cfg["layers"]] if "layers" in cfg
+                     else ["llama"] * layers)
+            attn_flops = kept = 0.0
+            for k in kinds:
+                if k == "delta":
+                    attn_flops += T * z["d_heads"] * 8 * z["d_dim"] * z["d_vdim"]
+                    kept += 2 * 4 * z["d_heads"] * z["d_dim"] * z["d_vdim"]
+                else:
+                    width = z["rank"] if k == "latent_attention" else z["dim"]
+                    keys = sum(min(i + 1, window) for i in range(T))
+                    attn_flops += 4.0 * keys * z["heads"] * width
+                    per_key = (z["rank"] if k == "latent_attention" else 2 * z["kv"] * z["dim"])
+                    kept += 2 * per_key * min(T, window)
+            rec = {"layers": layers, "weight_bytes": wbytes}
+            for b in (1, 8):
+                ms = run_prefill(engine, T, repeats=3, warmup=3, batch=b)
+                flops = b * (2 * T * (params - V * W) + 2 * V * W + attn_flops)
+                rec[f"prefill_b{b}_ms"] = ms
+                rec[f"prefill_b{b}_tok_s"] = b * T / (ms * 1e-3)
+                rec[f"prefill_b{b}_frac_bf16"] = flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+            for b in (1, 8, 64):
+                ms, _, per_step = run_decode(engine, b, min(args.steps, 128), args.warmup, T,
+                                             seed=b)
+                rec[f"decode_b{b}_ms"] = ms
+                rec[f"decode_b{b}_tok_s"] = b / (ms * 1e-3)
+                rec[f"decode_b{b}_frac_hbm"] = ((wbytes + b * kept) / (ms * 1e-3) / 1e9
+                                                / pk["hbm_gbs"])
+                rec["launches_per_step"] = per_step
+            rows[name] = rec
+            del engine
+            torch.cuda.empty_cache()
+    print(json.dumps({"design": "rigozen", "size": args.design_size, "sizes": z,
+                      "dtype": args.dtype, "prompt_len": T, "data": "synthetic",
+                      "weights": "random, seed 99", "peaks": pk, "models": rows,
+                      "clocks": clocks.result}))
+    return 0
+
+
 def reference_arm(args) -> int:
     """The unmodified reference (CuInfer), built from its own sources by
     ``baseline/reference_tools.py`` into ``baseline/_ref/cuinfer``, run through its stock command
@@ -391,8 +506,16 @@ def main() -> int:
                     help="skip the per-kernel shares of the decode step")
     ap.add_argument("--unequal", action="store_true",
                     help="prompts of unequal lengths 256..2,048 instead of 2,048 each")
+    ap.add_argument("--design", default=None, choices=["rigozen"],
+                    help="measure this design at real layer sizes beside Llama at the same "
+                         "sizes instead of the headline (another JSON line)")
+    ap.add_argument("--design-size", default="m", choices=sorted(DESIGN_SIZES))
     args = ap.parse_args()
 
+    if args.design:
+        if args.warmup < 3:
+            args.warmup = 3
+        return design_bench(args)
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:

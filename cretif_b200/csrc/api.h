@@ -35,9 +35,9 @@ int cretif_rope_kv_append(void* qkv, int ld, int dt, const float* cos_t, const f
                           unsigned int* fault, void* stream);
 
 // h[r, :] += y[r, :] * weight * rsqrt(mean(y[r]^2) + eps): a norm on a sublayer's output, fused
-// with the residual addition (32-bit).
+// with the residual addition (32-bit).  x_out (bfloat16 [R, H], may be null) receives the new rows.
 int cretif_rmsnorm_add(float* h, const void* y, int y_dt, int ldy, const float* weight, int R,
-                       int H, float eps, void* stream);
+                       int H, float eps, void* x_out, void* stream);
 
 // out = h converted to the element type out_dt (the stream handed to a sublayer without a norm).
 int cretif_convert_rows(const float* h, void* out, int out_dt, long long total, void* stream);
@@ -63,10 +63,12 @@ int cretif_delta_prepare(const float* proj, int ldp, float* prep, int ldo, const
 int cretif_delta_conv_state(const float* proj, int ldp, float* conv_state, long long state_stride,
                             int taps, int C, const int* cu_seqlens, const int* seq_slot, int B,
                             void* stream);
+// o_raw: float32 scratch [T, H e] for the read-outs before their norm.
 int cretif_delta_recurrence(const float* prep, int ldp, const float* gate, int ldg, float* state,
                             long long state_stride, const int* cu_seqlens, const int* seq_slot,
                             int B, int H, int G, int d, int e, const float* norm_w, float eps,
-                            void* out, int out_dt, int ldo, int write_state, void* stream);
+                            float* o_raw, void* out, int out_dt, int ldo, int write_state, int T,
+                            void* stream);
 
 // After a decode step: ids <- sampled (if given), positions and lengths + 1.
 int cretif_advance_decode(int* tok_ids, int* tok_pos, int* seq_start, const int* sampled, int B,
@@ -81,6 +83,12 @@ int cretif_gemm_simt(const void* A, int a_dt, const void* W, int w_dt, void* C, 
 int cretif_gemm_simt_batched(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt,
                              int M, int N, int K, int lda, int ldw, int ldc, int batch,
                              long long sa, long long sw, long long sc, void* stream);
+
+// The same batch in bfloat16 on the tensor cores (mma.sync through the warp-level matrix API):
+// W is [batch, N, K] contiguous, A and C rows have strides lda and ldc and product z starts at
+// A + z*sa and C + z*sc.  Any M, N, K.
+int cretif_gemm_heads(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldc,
+                      int batch, long long sa, long long sc, void* stream);
 
 // C[M,N] (= or +=) X[M,K] · W[N,K]^T for M <= 64 rows, bfloat16 operands, streaming W once.
 // K and the row strides must be multiples of 8 and the operands 16-byte aligned.
@@ -174,6 +182,8 @@ int cretif_fused_qkv_rope(const float* H, const float* norm_w, float eps, const 
 int cretif_fused_gate_up_silu(const float* H, const float* norm_w, float eps, const void* Wgu,
                               int ldw, void* act, int I, int gu_block, int M, int K,
                               unsigned int* fault, void* stream);
+int cretif_fused_gate_up_silu_x(const void* X, int ldx, const void* Wgu, int ldw, void* act, int I,
+                                int gu_block, int M, int K, unsigned int* fault, void* stream);
 int cretif_fused_smem_ok(int M, int K, int norm_prologue);
 // The three switches below exist so that tests can run both variants of a kernel on one
 // shape; an ordinary run never touches them.

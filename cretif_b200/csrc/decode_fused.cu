@@ -252,6 +252,22 @@ extern "C" int cretif_fused_gate_up_silu(const float* H, const float* norm_w, fl
   return dispatch_nt<kProNorm, kEpiSilu>(p, (I + 7) / 8, (cudaStream_t)stream);
 }
 
+// The same from rows that are already in bfloat16 (a feed-forward that reads the stream itself,
+// without a norm in front of it).
+extern "C" int cretif_fused_gate_up_silu_x(const void* X, int ldx, const void* Wgu, int ldw,
+                                           void* act, int I, int gu_block, int M, int K,
+                                           unsigned int* fault, void* stream) {
+  if (M <= 0) return kOk;
+  FusedParams p = {};
+  p.W = (const __nv_bfloat16*)Wgu; p.M = M; p.N = 2 * I; p.K = K; p.ldw = ldw;
+  p.X = (const __nv_bfloat16*)X; p.ldx = ldx;
+  p.act = (__nv_bfloat16*)act; p.I = I; p.gu_block = gu_block; p.fault = fault;
+  if (!common_ok(p) || !derive_fields(p) || !X || ldx % 8 || ldx < K || (((uintptr_t)X) & 15) ||
+      I <= 0 || gu_block < 0 || (gu_block && (I % gu_block || gu_block % 8)))
+    return kBadArgument;
+  return dispatch_nt<kProPlain, kEpiSilu>(p, (I + 7) / 8, (cudaStream_t)stream);
+}
+
 extern "C" int cretif_variant_count(int v) {
   return v >= 0 && v < kVarCount ? g_variant_counts[v] : -1;
 }

@@ -5,17 +5,20 @@
 // so the read-out sees the token's own write.  Three kernels serve any step shape (whole
 // prompts, further chunks at a cached position, single tokens), all arithmetic in 32-bit:
 //
-// * delta_prepare (a CTA per token): the causal convolution over time of the projected q, k
+// * delta_prepare (a warp per head of a token): the causal convolution over time of the projected q, k
 //   and v channels (taps from this step's rows, or from the sequence's saved last inputs where
 //   the window reaches back before the step), SiLU, unit length per q/k head (and the query's
 //   d^-1/2), beta = sigmoid(.), g = exp(-exp(A_log) softplus(. + dt_bias)).
-// * delta_recurrence (a CTA per (sequence, head)): the columns of M are independent, so a
-//   group of P lanes owns one column, each lane a slice of its d rows in registers; a token
+// * delta_recurrence (a CTA per (sequence, head, slice of columns)): the columns of M are
+//   independent, so the launcher cuts a head's columns into slices while the chip is not full,
+//   and within a CTA a group of P lanes owns one column, each lane a contiguous slice of its d rows in registers
+//   (the token's key and query slices come from shared memory in 16-byte pieces); a token
 //   costs two P-lane shuffle reductions and no barrier.  Tokens go in chunks of 16 whose
-//   operands are staged in shared memory; after a chunk the warps norm its outputs over e
-//   (RMS, weight, times SiLU of the gate) and store them.  The state is read once and written
+//   operands arrive in shared memory by asynchronous copies a chunk ahead (two stages).  The
+//   read-outs leave in 32-bit; delta_out_norm (a warp per token and head) norms them over e
+//   (RMS, weight, times SiLU of the gate).  The state is read once and written
 //   once per step.
-// * delta_conv_state (a CTA per sequence): the last taps-1 inputs of every channel, for the
+// * delta_conv_state (a thread per channel): the last taps-1 inputs of every channel, for the
 //   next step.
 #include "api.h"
 #include "common.cuh"
@@ -27,7 +30,14 @@ __device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : l
 
 // proj row: [q (G d) | k (G d) | v (H e) | gate (H e) | b (H) | a (H)]
 // prep row: [q (G d) | k (G d) | v (H e) | beta (H) | g (H)]
-__global__ void __launch_bounds__(256)
+// A warp per unit of a token's work: one of the 2G query/key heads (its d channels stay in the
+// lanes' registers between the convolution and the scaling to unit length, d <= 256), one of the
+// H value heads, or the token's H pairs of gates.  gridDim.y CTAs of eight warps share a token,
+// so that a step of one token is still a few dozen warps with all their loads in flight.
+constexpr int kPrepWarps = 8;
+constexpr int kPrepMaxD = 256;
+
+__global__ void __launch_bounds__(kPrepWarps * 32)
 delta_prepare_kernel(const float* __restrict__ proj, int ldp, float* __restrict__ prep, int ldo,
                      const float* __restrict__ conv_w, int taps,
                      const float* __restrict__ conv_state, size_t state_stride,
@@ -35,165 +45,254 @@ delta_prepare_kernel(const float* __restrict__ proj, int ldp, float* __restrict_
                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                      const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int H,
                      int G, int d, int e, float unit_eps) {
-  extern __shared__ float ch[];                  // the token's q, k, v channels after SiLU
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
+  const int unit = blockIdx.y * kPrepWarps + warp;
+  if (unit >= 2 * G + H + 1) return;
   const int b = tok_seq[t];
   const int lt = tok_pos[t] - seq_start[b];      // tokens of this sequence before t in the step
   const int C = 2 * G * d + H * e;
   const float* st = conv_state + (size_t)seq_slot[b] * state_stride;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  const float* row = proj + (size_t)t * ldp;
+  float* out = prep + (size_t)t * ldo;
+  auto conv = [&](int c) {                        // the convolution over time and SiLU
     float acc = 0.f;
-    for (int i = 0; i < taps; ++i) {             // i tokens back
+#pragma unroll 4
+    for (int i = 0; i < taps; ++i) {              // i tokens back
       const float w = conv_w[(size_t)c * taps + (taps - 1 - i)];
-      const float z = i <= lt ? proj[(size_t)(t - i) * ldp + c]
+      const float z = i <= lt ? row[c - (ptrdiff_t)i * ldp]
                               : st[(size_t)c * (taps - 1) + (taps - 1) - (i - lt)];
       acc = fmaf(w, z, acc);
     }
-    ch[c] = silu_f32(acc);
-  }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  float* out = prep + (size_t)t * ldo;
-  for (int head = warp; head < 2 * G; head += nwarps) {      // q heads, then k heads
-    const float* x = ch + (size_t)head * d;
+    return silu_f32(acc);
+  };
+  if (unit < 2 * G) {                             // a query head (unit < G) or a key head
+    const int c0 = unit * d;
+    float val[kPrepMaxD / 32];
     float ss = 0.f;
-    for (int i = lane; i < d; i += 32) ss += x[i] * x[i];
+#pragma unroll
+    for (int m = 0; m < kPrepMaxD / 32; ++m) {
+      const int i = lane + 32 * m;
+      val[m] = i < d ? conv(c0 + i) : 0.f;
+      ss += val[m] * val[m];
+    }
     ss = warp_sum(ss);
     float f = 1.0f / sqrtf(ss + unit_eps);
-    if (head < G) f *= 1.0f / sqrtf((float)d);
-    for (int i = lane; i < d; i += 32) out[(size_t)head * d + i] = x[i] * f;
-  }
-  for (int i = threadIdx.x; i < H * e; i += blockDim.x) out[2 * G * d + i] = ch[2 * G * d + i];
-  const float* row = proj + (size_t)t * ldp;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    const float bz = row[C + H * e + h], az = row[C + H * e + H + h];
-    out[C + h] = 1.0f / (1.0f + expf(-bz));
-    out[C + H + h] = expf(-expf(a_log[h]) * softplus_f32(az + dt_bias[h]));
+    if (unit < G) f *= 1.0f / sqrtf((float)d);
+#pragma unroll
+    for (int m = 0; m < kPrepMaxD / 32; ++m) {
+      const int i = lane + 32 * m;
+      if (i < d) out[c0 + i] = val[m] * f;
+    }
+  } else if (unit < 2 * G + H) {                  // a value head
+    const int c0 = 2 * G * d + (unit - 2 * G) * e;
+#pragma unroll 4
+    for (int i = lane; i < e; i += 32) out[c0 + i] = conv(c0 + i);
+  } else {                                        // the gates
+    for (int h = lane; h < H; h += 32) {
+      const float bz = row[C + H * e + h], az = row[C + H * e + H + h];
+      out[C + h] = 1.0f / (1.0f + expf(-bz));
+      out[C + H + h] = expf(-expf(a_log[h]) * softplus_f32(az + dt_bias[h]));
+    }
   }
 }
 
+// A thread per channel: the last taps-1 inputs after this step.
 __global__ void delta_conv_state_kernel(const float* __restrict__ proj, int ldp,
                                         float* __restrict__ conv_state, size_t state_stride,
                                         int taps, int C, const int* __restrict__ cu_seqlens,
                                         const int* __restrict__ seq_slot) {
   const int b = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
   const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
-  float* st = conv_state + (size_t)seq_slot[b] * state_stride;
   const int keep = taps - 1;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float* s = st + (size_t)c * keep;
-    for (int j = 0; j < keep; ++j) {             // ascending: reads run ahead of writes
-      const int back = keep - j;                 // this entry is `back` tokens before the next
-      s[j] = back <= n ? proj[(size_t)(t0 + n - back) * ldp + c] : s[j + n];
-    }
+  float* s = conv_state + (size_t)seq_slot[b] * state_stride + (size_t)c * keep;
+  for (int j = 0; j < keep; ++j) {               // ascending: reads run ahead of writes
+    const int back = keep - j;                   // this entry is `back` tokens before the next
+    s[j] = back <= n ? proj[(size_t)(t0 + n - back) * ldp + c] : s[j + n];
   }
 }
 
 constexpr int kChunk = 16;
 
-template <int DREG, typename TO>
-__global__ void __launch_bounds__(1024)
-delta_recurrence_kernel(const float* __restrict__ prep, int ldp, const float* __restrict__ gate,
-                        int ldg, float* __restrict__ state, size_t state_stride,
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(src) : "memory");
+}
+
+template <int DREG, int MAXT>
+__global__ void __launch_bounds__(MAXT)
+delta_recurrence_kernel(const float* __restrict__ prep, int ldp, float* __restrict__ state,
+                        size_t state_stride,
                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
-                        int H, int G, int d, int e, int P, const float* __restrict__ norm_w,
-                        float eps, TO* __restrict__ out, int ldo, int write_state) {
-  extern __shared__ float sm[];
+                        int H, int G, int d, int e, int P, int ecols, float* __restrict__ o_raw,
+                        int write_state) {
+  extern __shared__ __align__(16) float sm[];
+  // with at most 512 threads a lane also keeps the token's key slice in registers between
+  // the two passes over its rows
+  constexpr bool kKeepK = MAXT <= 512 && DREG <= 32;
   const int b = blockIdx.x, h = blockIdx.y, grp = h / (H / G);
-  const int dpad = P * DREG;
-  float* qs = sm;                                // [kChunk][dpad]
-  float* ks = qs + kChunk * dpad;                // [kChunk][dpad]
-  float* vs = ks + kChunk * dpad;                // [kChunk][e]
-  float* os = vs + kChunk * e;                   // [kChunk][e]
-  float* bs = os + kChunk * e;                   // [kChunk] beta
-  float* gs = bs + kChunk;                       // [kChunk] decay
-  const int tid = threadIdx.x, part = tid % P, j = tid / P;
-  const bool active = j < e;
+  // lane `part` owns rows part*DREG .. +DREG-1; its slice of a staged key or query starts at
+  // part*kSlice floats (four more than it holds, so that the P slices a warp reads at once
+  // lie in different banks)
+  constexpr int kSlice = DREG + 4;
+  const int dpad = P * kSlice;
+  // two stages of a chunk's operands, filled by asynchronous copies a chunk ahead:
+  // q, k [kChunk][dpad], v [kChunk][ecols], beta, decay [kChunk]
+  const int stage_floats = kChunk * (2 * dpad + ecols + 2);
+  // this CTA owns columns col0 .. col0 + ecols - 1 of the head's matrix
+  const int col0 = blockIdx.z * ecols;
+  const int tid = threadIdx.x, part = tid % P, jl = tid / P, j = col0 + jl;
+  const bool active = jl < ecols;
   float* M = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e;
   float S[DREG];
 #pragma unroll
   for (int r = 0; r < DREG; ++r) {
-    const int i = part + P * r;
+    const int i = part * DREG + r;
     S[r] = (active && i < d) ? M[(size_t)i * e + j] : 0.f;
   }
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
   const int C = 2 * G * d + H * e;
-  const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
-  for (int c0 = t0; c0 < t1; c0 += kChunk) {
+  // the padding of the key and query slices stays zero for good
+  for (int idx = tid; idx < 2 * stage_floats; idx += blockDim.x) sm[idx] = 0.f;
+  __syncthreads();
+  auto issue = [&](int s, int c0) {               // a chunk's operands on their way to stage s
+    float* qs = sm + s * stage_floats;
+    float* ks = qs + kChunk * dpad;
+    float* vs = ks + kChunk * dpad;
+    float* bs = vs + kChunk * ecols;
     const int n = min(kChunk, t1 - c0);
-    for (int idx = tid; idx < n * dpad; idx += blockDim.x) {
-      const int tt = idx / dpad, i = idx - tt * dpad;
+    for (int idx = tid; idx < n * d; idx += blockDim.x) {
+      const int tt = idx / d, i = idx - tt * d;
+      const int at = tt * dpad + (i / DREG) * kSlice + (i % DREG);
       const float* row = prep + (size_t)(c0 + tt) * ldp;
-      qs[idx] = i < d ? row[(size_t)grp * d + i] : 0.f;
-      ks[idx] = i < d ? row[(size_t)(G + grp) * d + i] : 0.f;
+      cp_async4(qs + at, row + (size_t)grp * d + i);
+      cp_async4(ks + at, row + (size_t)(G + grp) * d + i);
     }
-    for (int idx = tid; idx < n * e; idx += blockDim.x) {
-      const int tt = idx / e, i = idx - tt * e;
-      vs[idx] = prep[(size_t)(c0 + tt) * ldp + 2 * G * d + (size_t)h * e + i];
+    for (int idx = tid; idx < n * ecols; idx += blockDim.x) {
+      const int tt = idx / ecols, i = idx - tt * ecols;
+      cp_async4(vs + idx, prep + (size_t)(c0 + tt) * ldp + 2 * G * d + (size_t)h * e + col0 + i);
     }
     if (tid < n) {
-      bs[tid] = prep[(size_t)(c0 + tid) * ldp + C + h];
-      gs[tid] = prep[(size_t)(c0 + tid) * ldp + C + H + h];
+      cp_async4(bs + tid, prep + (size_t)(c0 + tid) * ldp + C + h);
+      cp_async4(bs + kChunk + tid, prep + (size_t)(c0 + tid) * ldp + C + H + h);
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (t0 < t1) issue(0, t0);
+  int s = 0;
+  for (int c0 = t0; c0 < t1; c0 += kChunk, s ^= 1) {
+    const int n = min(kChunk, t1 - c0);
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();          // stage s has arrived; the other stage is read no more
+    if (c0 + kChunk < t1) issue(s ^ 1, c0 + kChunk);
+    const float* qs = sm + s * stage_floats;
+    const float* ks = qs + kChunk * dpad;
+    const float* vs = ks + kChunk * dpad;
+    const float* bs = vs + kChunk * ecols;
+    const float* gs = bs + kChunk;
     for (int tt = 0; tt < n; ++tt) {
-      const float* kk = ks + tt * dpad + part;
-      const float* qq = qs + tt * dpad + part;
+      const float4* k4 = reinterpret_cast<const float4*>(ks + tt * dpad + part * kSlice);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + tt * dpad + part * kSlice);
       const float g = gs[tt];
-      float r = 0.f;
+      float kreg[kKeepK ? DREG : 4];
+      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-      for (int x = 0; x < DREG; ++x) r = fmaf(S[x], kk[P * x], r);
-      for (int o = P >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-      const float u = bs[tt] * ((active ? vs[tt * e + j] : 0.f) - g * r);
-      float acc = 0.f;
-#pragma unroll
-      for (int x = 0; x < DREG; ++x) {
-        S[x] = fmaf(kk[P * x], u, g * S[x]);
-        acc = fmaf(S[x], qq[P * x], acc);
+      for (int x = 0; x < DREG; x += 4) {
+        const float4 kv = k4[x >> 2];
+        if (kKeepK) { kreg[x] = kv.x; kreg[x + 1] = kv.y; kreg[x + 2] = kv.z; kreg[x + 3] = kv.w; }
+        r0 = fmaf(S[x], kv.x, r0);
+        r1 = fmaf(S[x + 1], kv.y, r1);
+        r2 = fmaf(S[x + 2], kv.z, r2);
+        r3 = fmaf(S[x + 3], kv.w, r3);
       }
+      float r = (r0 + r1) + (r2 + r3);
+      for (int o = P >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+      const float u = bs[tt] * ((active ? vs[tt * ecols + jl] : 0.f) - g * r);
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int x = 0; x < DREG; x += 4) {
+        float4 kv;
+        if (kKeepK) kv = make_float4(kreg[x], kreg[x + 1], kreg[x + 2], kreg[x + 3]);
+        else kv = k4[x >> 2];
+        const float4 qv = q4[x >> 2];
+        S[x] = fmaf(kv.x, u, g * S[x]);
+        S[x + 1] = fmaf(kv.y, u, g * S[x + 1]);
+        S[x + 2] = fmaf(kv.z, u, g * S[x + 2]);
+        S[x + 3] = fmaf(kv.w, u, g * S[x + 3]);
+        a0 = fmaf(S[x], qv.x, a0);
+        a1 = fmaf(S[x + 1], qv.y, a1);
+        a2 = fmaf(S[x + 2], qv.z, a2);
+        a3 = fmaf(S[x + 3], qv.w, a3);
+      }
+      float acc = (a0 + a1) + (a2 + a3);
       for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (active && part == 0) os[tt * e + j] = acc;
+      if (active && part == 0) o_raw[(size_t)(c0 + tt) * H * e + (size_t)h * e + j] = acc;
     }
-    __syncthreads();
-    for (int tt = warp; tt < n; tt += nwarps) {       // the chunk's outputs, a warp per token
-      const float* o = os + tt * e;
-      float ss = 0.f;
-      for (int i = lane; i < e; i += 32) ss += o[i] * o[i];
-      ss = warp_sum(ss);
-      const float inv = 1.0f / sqrtf(ss / (float)e + eps);
-      const float* grow = gate + (size_t)(c0 + tt) * ldg + (size_t)h * e;
-      TO* orow = out + (size_t)(c0 + tt) * ldo + (size_t)h * e;
-      for (int i = lane; i < e; i += 32)
-        orow[i] = from_float<TO>(o[i] * inv * norm_w[i] * silu_f32(grow[i]));
-    }
-    __syncthreads();
   }
   if (write_state) {
 #pragma unroll
     for (int r = 0; r < DREG; ++r) {
-      const int i = part + P * r;
+      const int i = part * DREG + r;
       if (active && i < d) M[(size_t)i * e + j] = S[r];
     }
   }
 }
 
-template <int DREG, typename TO>
-static int launch_recurrence(const float* prep, int ldp, const float* gate, int ldg, float* state,
-                             size_t state_stride, const int* cu, const int* seq_slot, int B, int H,
-                             int G, int d, int e, int P, const float* norm_w, float eps, void* out,
-                             int ldo, int write_state, cudaStream_t st) {
-  const int threads = ((e * P + 31) / 32) * 32;
-  const size_t smem = sizeof(float) * ((size_t)kChunk * (2 * P * DREG + 2 * e) + 2 * kChunk);
-  auto kern = delta_recurrence_kernel<DREG, TO>;
+// The read-outs of every (token, head), a warp each: RMS norm over e, the weight, SiLU of the gate.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+delta_out_norm_kernel(const float* __restrict__ o_raw, const float* __restrict__ gate, int ldg,
+                      const float* __restrict__ norm_w, float eps, TO* __restrict__ out, int ldo,
+                      int H, int e, long long items) {
+  const long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = item / H;
+  const int h = (int)(item - t * H);
+  const float* o = o_raw + (size_t)t * H * e + (size_t)h * e;
+  const float* grow = gate + (size_t)t * ldg + (size_t)h * e;
+  TO* orow = out + (size_t)t * ldo + (size_t)h * e;
+  float ss = 0.f;
+#pragma unroll 4
+  for (int i = lane; i < e; i += 32) ss += o[i] * o[i];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)e + eps);
+#pragma unroll 4
+  for (int i = lane; i < e; i += 32)
+    orow[i] = from_float<TO>(o[i] * inv * norm_w[i] * silu_f32(grow[i]));
+}
+
+template <int DREG, int MAXT>
+static int launch_recurrence_t(const float* prep, int ldp, float* state, size_t state_stride,
+                               const int* cu, const int* seq_slot, int B, int H, int G, int d,
+                               int e, int P, int ecols, float* o_raw, int write_state, int threads,
+                               cudaStream_t st) {
+  const size_t stage = (size_t)kChunk * (2 * P * (DREG + 4) + ecols + 2);
+  const size_t smem = sizeof(float) * 2 * stage;
+  auto kern = delta_recurrence_kernel<DREG, MAXT>;
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return kBadArgument;
     cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
-  kern<<<dim3(B, H), threads, smem, st>>>(prep, ldp, gate, ldg, state, state_stride, cu, seq_slot,
-                                          H, G, d, e, P, norm_w, eps, (TO*)out, ldo, write_state);
+  kern<<<dim3(B, H, e / ecols), threads, smem, st>>>(prep, ldp, state, state_stride, cu, seq_slot,
+                                                     H, G, d, e, P, ecols, o_raw, write_state);
   return launch_status();
+}
+
+template <int DREG>
+static int launch_recurrence(const float* prep, int ldp, float* state, size_t state_stride,
+                             const int* cu, const int* seq_slot, int B, int H, int G, int d, int e,
+                             int P, int ecols, float* o_raw, int write_state, cudaStream_t st) {
+  const int threads = ((ecols * P + 31) / 32) * 32;
+  if (threads <= 512)
+    return launch_recurrence_t<DREG, 512>(prep, ldp, state, state_stride, cu, seq_slot, B, H, G, d,
+                                          e, P, ecols, o_raw, write_state, threads, st);
+  return launch_recurrence_t<DREG, 1024>(prep, ldp, state, state_stride, cu, seq_slot, B, H, G, d,
+                                         e, P, ecols, o_raw, write_state, threads, st);
 }
 
 }  // namespace cretif
@@ -210,14 +309,11 @@ extern "C" int cretif_delta_prepare(const float* proj, int ldp, float* prep, int
   if (H <= 0 || G <= 0 || H % G || d <= 0 || e <= 0 || taps < 1) return kBadArgument;
   const int C = 2 * G * d + H * e;
   if (ldp < C + H * e + 2 * H || ldo < C + 2 * H) return kBadArgument;
-  const size_t smem = sizeof(float) * (size_t)C;
-  if (smem > 200 * 1024) return kBadArgument;
-  if (smem > 48 * 1024) {
-    cudaError_t err = cudaFuncSetAttribute(delta_prepare_kernel,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (err != cudaSuccess) return (int)err;
-  }
-  delta_prepare_kernel<<<T, 256, smem, (cudaStream_t)stream>>>(
+  if (d > kPrepMaxD) return kBadArgument;
+  const int units = 2 * G + H + 1;
+  dim3 grid(T, (units + kPrepWarps - 1) / kPrepWarps);
+  if (grid.y > 65535) return kBadArgument;
+  delta_prepare_kernel<<<grid, kPrepWarps * 32, 0, (cudaStream_t)stream>>>(
       proj, ldp, prep, ldo, conv_w, taps, conv_state, (size_t)state_stride, a_log, dt_bias,
       tok_pos, tok_seq, seq_slot, seq_start, H, G, d, e, unit_eps);
   return launch_status();
@@ -229,7 +325,7 @@ extern "C" int cretif_delta_conv_state(const float* proj, int ldp, float* conv_s
                                        void* stream) {
   if (B <= 0 || taps <= 1) return kOk;
   if (C <= 0 || ldp < C) return kBadArgument;
-  delta_conv_state_kernel<<<B, 256, 0, (cudaStream_t)stream>>>(
+  delta_conv_state_kernel<<<dim3(B, (C + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       proj, ldp, conv_state, (size_t)state_stride, taps, C, cu_seqlens, seq_slot);
   return launch_status();
 }
@@ -238,31 +334,58 @@ extern "C" int cretif_delta_recurrence(const float* prep, int ldp, const float* 
                                        float* state, long long state_stride,
                                        const int* cu_seqlens, const int* seq_slot, int B, int H,
                                        int G, int d, int e, const float* norm_w, float eps,
-                                       void* out, int out_dt, int ldo, int write_state,
-                                       void* stream) {
-  if (B <= 0) return kOk;
-  if (H <= 0 || G <= 0 || H % G || d <= 0 || e <= 0 || e > 1024) return kBadArgument;
-  // P lanes share a column: enough that a lane holds at most 32 rows, as long as the CTA
-  // stays within 1024 threads; a lane then holds up to 128
+                                       float* o_raw, void* out, int out_dt, int ldo,
+                                       int write_state, int T, void* stream) {
+  if (B <= 0 || T <= 0) return kOk;
+  if (H <= 0 || G <= 0 || H % G || d <= 0 || e <= 0 || !o_raw) return kBadArgument;
+  if (out_dt != kF32 && out_dt != kBF16) return kBadDType;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  // P lanes share a column, each with d/P of its rows in registers: up to 32 rows a lane.
+  // Measured at d = e = 128 over 2,048 tokens of one sequence (16 heads, microseconds a layer):
+  // 32 rows a lane and 16 warps a CTA without slices of columns 2,560 (bound by the instructions
+  // issued: 276 a warp and token, 65 % of the issue slots); the same in slices of 32 columns
+  // 1,116 (a warp a scheduler: the chain of a token's dependent steps); 8 rows a lane 1,087
+  // (the shuffles and shared-memory reads share one pipe: about 1,000 of its cycles a token and
+  // head); 64 rows a lane 1,760 (two warps a CTA).  Eight sequences: 32 and 64 rows the same,
+  // 8 rows a sixth slower.
   int P = 1;
-  while (P < 32 && (d + P - 1) / P > 32 && ((e * 2 * P + 31) / 32) * 32 <= 1024) P *= 2;
+  while (P < 32 && (d + P - 1) / P > 32) P *= 2;
+  // The columns of a head's matrix are independent: a head's columns are cut into slices for
+  // CTAs of their own while the (sequence, head) pairs alone do not fill the chip twice over
+  // (down to 32 columns), and as far as a CTA's 1024 threads demand.
+  int ecols = e;
+  while ((long long)B * H * (e / ecols) < 2LL * sm_count && ecols % 2 == 0 && ecols / 2 >= 32)
+    ecols /= 2;
+  while (ecols * P > 1024 && ecols % 2 == 0 && ecols > 1) ecols /= 2;
+  while (ecols * P > 1024 && P > 1) P /= 2;            // an odd number of columns: longer slices
+  if (ecols * P > 1024) return kBadArgument;
   const int rows = (d + P - 1) / P;
   if (rows > 128) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
-#define CRETIF_DELTA(DREG)                                                                        \
-  (out_dt == kF32                                                                                 \
-       ? launch_recurrence<DREG, float>(prep, ldp, gate, ldg, state, (size_t)state_stride,       \
-                                        cu_seqlens, seq_slot, B, H, G, d, e, P, norm_w, eps, out, \
-                                        ldo, write_state, st)                                     \
-       : launch_recurrence<DREG, __nv_bfloat16>(prep, ldp, gate, ldg, state,                     \
-                                                (size_t)state_stride, cu_seqlens, seq_slot, B, H, \
-                                                G, d, e, P, norm_w, eps, out, ldo, write_state,   \
-                                                st))
-  if (out_dt != kF32 && out_dt != kBF16) return kBadDType;
-  if (rows <= 8) return CRETIF_DELTA(8);
-  if (rows <= 16) return CRETIF_DELTA(16);
-  if (rows <= 32) return CRETIF_DELTA(32);
-  if (rows <= 64) return CRETIF_DELTA(64);
-  return CRETIF_DELTA(128);
+  int rc;
+#define CRETIF_DELTA(DREG)                                                                      \
+  launch_recurrence<DREG>(prep, ldp, state, (size_t)state_stride, cu_seqlens, seq_slot, B, H, G, \
+                          d, e, P, ecols, o_raw, write_state, st)
+  if (rows <= 8) rc = CRETIF_DELTA(8);
+  else if (rows <= 16) rc = CRETIF_DELTA(16);
+  else if (rows <= 32) rc = CRETIF_DELTA(32);
+  else if (rows <= 64) rc = CRETIF_DELTA(64);
+  else rc = CRETIF_DELTA(128);
 #undef CRETIF_DELTA
+  if (rc) return rc;
+  const long long items = (long long)T * H;
+  const unsigned blocks = (unsigned)((items + 7) / 8);
+  if (out_dt == kF32)
+    delta_out_norm_kernel<float><<<blocks, 256, 0, st>>>(o_raw, gate, ldg, norm_w, eps,
+                                                         (float*)out, ldo, H, e, items);
+  else
+    delta_out_norm_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+        o_raw, gate, ldg, norm_w, eps, (__nv_bfloat16*)out, ldo, H, e, items);
+  return launch_status();
 }

@@ -213,9 +213,19 @@ def gemm_simt(a, w, c, accumulate: bool = False) -> None:
                                   _stream()), "gemm_simt")
 
 
+_batched_simt_only = False
+
+
+def batched_products_simt_only(on: bool) -> None:
+    """(For tests that run both.)  Keep bfloat16 batched products off the tensor cores."""
+    global _batched_simt_only
+    _batched_simt_only = bool(on)
+
+
 def gemm_batched(a, w, c) -> None:
     """c[:, z, :] = a[:, z, :] · w[z]ᵀ for every z: ``a`` [M, Z, K], ``w`` [Z, N, K], ``c``
-    [M, Z, N] (a matrix per head applied to that head's slice of every row), 32-bit FMA."""
+    [M, Z, N] (a matrix per head applied to that head's slice of every row): bfloat16 on the
+    tensor cores, float32 by 32-bit FMA."""
     _need(a, "a", dim=3); _need(w, "w", dim=3); _need(c, "c", dim=3)
     M, Z, K = a.shape
     N = w.shape[1]
@@ -224,6 +234,12 @@ def gemm_batched(a, w, c) -> None:
                           f"{tuple(c.shape)}")
     if a.stride(2) != 1 or c.stride(2) != 1 or not w.is_contiguous():
         raise KernelError("gemm_batched: rows must be dense and w contiguous")
+    if a.dtype == w.dtype == c.dtype == torch.bfloat16 and not _batched_simt_only:
+        _check(lib().cretif_gemm_heads(
+            _p(a), _p(w), _p(c), M, N, K, a.stride(0), c.stride(0), Z,
+            ctypes.c_longlong(a.stride(1)), ctypes.c_longlong(c.stride(1)), _stream()),
+            "gemm_heads")
+        return
     _check(lib().cretif_gemm_simt_batched(
         _p(a), _dt(a), _p(w), _dt(w), _p(c), _dt(c), M, N, K, a.stride(0), K, c.stride(0), Z,
         ctypes.c_longlong(a.stride(1)), ctypes.c_longlong(N * K), ctypes.c_longlong(c.stride(1)),
@@ -231,14 +247,19 @@ def gemm_batched(a, w, c) -> None:
 
 
 # ------------------------------------------------------------------ norms beside the sublayers
-def rmsnorm_add(h, y, weight, eps: float) -> None:
-    """h += y * weight * rsqrt(mean(y²) + eps), row by row, in 32-bit."""
+def rmsnorm_add(h, y, weight, eps: float, x_out=None) -> None:
+    """h += y * weight * rsqrt(mean(y²) + eps), row by row, in 32-bit.  ``x_out`` (bfloat16,
+    optional) receives the new rows of ``h`` for the sublayer that reads the stream next."""
     _need(h, "h", torch.float32, 2); _need(y, "y", dim=2); _need(weight, "weight", torch.float32, 1)
     R, H = h.shape
     if tuple(y.shape) != (R, H) or not h.is_contiguous() or weight.numel() != H:
         raise KernelError("rmsnorm_add: y must match h and weight have H elements")
+    if x_out is not None:
+        _need(x_out, "x_out", torch.bfloat16, 2)
+        if tuple(x_out.shape) != (R, H) or not x_out.is_contiguous():
+            raise KernelError("rmsnorm_add: x_out must be a contiguous copy of h's shape")
     _check(lib().cretif_rmsnorm_add(_p(h), _p(y), _dt(y), _rows(y, "y"), _p(weight), R, H,
-                                    ctypes.c_float(eps), _stream()), "rmsnorm_add")
+                                    ctypes.c_float(eps), _p(x_out), _stream()), "rmsnorm_add")
 
 
 def convert_rows(h, out) -> None:
@@ -315,11 +336,13 @@ def delta_recurrence(prep, gate, state, cu_seqlens, seq_slot, B: int, H: int, G:
     _need(norm_w, "norm_w", torch.float32, 1)
     if state.stride(1) != 1 or state.shape[1] != H * d * e or norm_w.numel() != e:
         raise KernelError("delta_recurrence: the state's sizes do not fit")
+    T = prep.shape[0]
+    o_raw = torch.empty((T, H * e), dtype=torch.float32, device=prep.device)
     _check(lib().cretif_delta_recurrence(
         _p(prep), _rows(prep, "prep"), _p(gate), _rows(gate, "gate"), _p(state),
         ctypes.c_longlong(state.stride(0)), _p(cu_seqlens), _p(seq_slot), B, H, G, d, e,
-        _p(norm_w), ctypes.c_float(eps), _p(out), _dt(out), _rows(out, "out"), int(write_state),
-        _stream()), "delta_recurrence")
+        _p(norm_w), ctypes.c_float(eps), _p(o_raw), _p(out), _dt(out), _rows(out, "out"),
+        int(write_state), T, _stream()), "delta_recurrence", kernels=2)
 
 
 # ------------------------------------------------------------------ attention
@@ -642,6 +665,33 @@ def fused_linear_add(x, w, h) -> None:
     _check(lib().cretif_fused_linear(_p(x), _rows(x, "x"), None, None, None, ctypes.c_float(0.0),
                                      _p(w), _rows(w, "w"), _p(h), F32, _rows(h, "h"), 1, M, N, K,
                                      _p(fault_word(h.device)), _stream()), "fused_linear_add")
+
+
+def fused_linear_x(x, w, out, accumulate: bool = False) -> None:
+    """out (+)= x · wᵀ with the few-token kernels (x bfloat16; out bfloat16, or float32 which may
+    be added to)."""
+    _need(x, "x", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 2); _need(out, "out", dim=2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError("fused_linear_x: shapes do not fit")
+    _check(lib().cretif_fused_linear(_p(x), _rows(x, "x"), None, None, None, ctypes.c_float(0.0),
+                                     _p(w), _rows(w, "w"), _p(out), _dt(out), _rows(out, "out"),
+                                     int(accumulate), M, N, K, _p(fault_word(x.device)),
+                                     _stream()), "fused_linear_x")
+
+
+def fused_gate_up_silu_x(x, w_gu, act, block: int = 0) -> None:
+    """act = silu(x·Wgᵀ) ⊙ (x·Wuᵀ) from bfloat16 rows, one few-token kernel."""
+    _need(x, "x", torch.bfloat16, 2); _need(w_gu, "w_gu", torch.bfloat16, 2)
+    _need(act, "act", torch.bfloat16, 2)
+    M, K = x.shape
+    I = act.shape[1]
+    if tuple(w_gu.shape) != (2 * I, K) or act.shape[0] != M or not act.is_contiguous():
+        raise KernelError("fused_gate_up_silu_x: shapes do not fit")
+    _check(lib().cretif_fused_gate_up_silu_x(_p(x), _rows(x, "x"), _p(w_gu), _rows(w_gu, "w_gu"),
+                                             _p(act), I, block, M, K, _p(fault_word(x.device)),
+                                             _stream()), "fused_gate_up_silu_x")
 
 
 def fused_qkv_rope(h, norm_w, eps: float, w_qkv, q_out, cos, sin, pairing: int, nh: int,

@@ -165,7 +165,8 @@ class Attention(Part):
         if self.qk_norm is not None:
             # norms over the whole projections; the kernel that norms the keys stores them
             # (and, when the values are the keys, the un-normed columns as values)
-            qkv = linear(x, self.w_qkv)
+            from .linear import linear_few
+            qkv = linear_few(x, self.w_qkv)
             if not self.values_are_keys and cache.writes:
                 ops.rope_kv_append(qkv, None, None, 0, 0, self.nh, self.nkv, self.hd,
                                    ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.table, kv.k,
@@ -201,6 +202,8 @@ class Attention(Part):
         if into is not None:
             linear(o, self.w_o, out=into, accumulate=True)
             return None
+        if self.qk_norm is not None:
+            return linear_few(o, self.w_o, out_dtype=torch.float32)
         return linear(o, self.w_o, out_dtype=torch.float32)
 
     def forward_from_residual(self, h, norm, ctx, cache) -> bool:

@@ -46,6 +46,9 @@ def call_part(branch, x, ctx, cache):
 
 @register_part("arrangement", "residual")
 def run_residual(layer, h, pending, ctx, caches):
+    # a copy of the stream in the compute type, left by the kernel that last added to it
+    extras = getattr(ctx, "extras", None)
+    lowp = extras.pop("stream_copy", None) if extras is not None else None
     for branch, cache in zip(layer.branches, caches):
         part = branch.part
         if (pending is None and branch.norm is not None and branch.post_norm is None
@@ -53,22 +56,29 @@ def run_residual(layer, h, pending, ctx, caches):
             took = (part.forward_from_residual(h, branch.norm, ctx, cache)
                     if branch.role == "mixer" else part.forward_from_residual(h, branch.norm, ctx))
             if took:
+                lowp = None
                 continue
         if branch.norm is not None:
             x = branch.norm.forward(h, pending)              # h += pending; x = norm(h)
+            if pending is not None:
+                lowp = None
             pending = None
         else:
             if pending is not None:
                 h.add_(pending)
-                pending = None
-            x = stream_as(h, part.dtype)                     # the part reads the stream itself
+                pending, lowp = None, None
+            # the part reads the stream itself
+            x = lowp if lowp is not None and lowp.dtype == part.dtype else stream_as(h, part.dtype)
         y = call_part(branch, x, ctx, cache)
         if branch.post_norm is not None:
             if hasattr(branch.post_norm, "add_into"):
-                branch.post_norm.add_into(h, y)              # h += norm(y), 32-bit, one kernel
+                # h += norm(y), 32-bit, one kernel, which also leaves the next reader's copy
+                lowp = branch.post_norm.add_into(h, y, emit=True)
                 continue
             y = branch.post_norm.forward(y.to(h.dtype).contiguous())
         pending = y
+    if lowp is not None and pending is None and extras is not None:
+        extras["stream_copy"] = lowp
     return pending
 
 

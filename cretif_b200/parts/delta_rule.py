@@ -24,7 +24,7 @@ from ..cache import StateRequest
 from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .base import Part, register_part
-from .linear import linear
+from .linear import linear_few as linear
 
 
 @register_part("mixer", "gated_delta_rule")

@@ -22,7 +22,7 @@ from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .attention import run_attention
 from .base import Part, register_part
-from .linear import linear
+from .linear import linear_few as linear
 
 
 @register_part("mixer", "latent_attention")

@@ -56,3 +56,25 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
             return out
     ops.gemm_simt(x, w, out, accumulate)
     return out
+
+
+FEW_ROWS = 64
+
+
+def linear_few(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+               out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
+    """``linear`` for parts that read rows which are already in the compute type: bfloat16
+    steps of at most 64 rows take the few-token kernels (weights streamed once through shared
+    memory or registers, launched as programmatic dependents), everything else ``linear``."""
+    from .attention import fused_steps_enabled
+    M, K = x.shape
+    if (0 < M <= FEW_ROWS and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and not _force_plain and fused_steps_enabled() and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and ops.fused_supported(M, K, w, norm=False)):
+        if out is None:
+            out = torch.empty((M, w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+        if out.dtype == torch.float32 or not accumulate:
+            ops.fused_linear_x(x, w, out, accumulate)
+            return out
+    return linear(x, w, out_dtype=out_dtype, out=out, accumulate=accumulate)

@@ -53,8 +53,17 @@ class GatedMLP(Part):
     def forward(self, x, ctx, into=None):
         """``into``: a float32 matrix that the output is added to (the residual stream) instead
         of being returned."""
+        from .attention import FUSED_MAX_TOKENS, fused_steps_enabled
+        from .linear import linear_few
         T = x.shape[0]
         act = torch.empty((T, self.inter), dtype=self.dtype, device=x.device)
+        if (T <= FUSED_MAX_TOKENS and self.dtype == torch.bfloat16 and into is None
+                and fused_steps_enabled() and not plain_forced() and x.is_contiguous()
+                and ops.fused_supported(T, self.hidden_size, self.w_gate_up, norm=False)
+                and ops.fused_supported(T, self.inter, self.w_down, norm=False)):
+            # few tokens that are already in bfloat16 (no norm in front of this part)
+            ops.fused_gate_up_silu_x(x, self.w_gate_up, act, self.gu_block)
+            return linear_few(act, self.w_down, out_dtype=torch.float32)
         if (self.gu_block == 64 and T > SKINNY_ROWS() and not plain_forced()
                 and ops.gemm_tc_supported(x, self.w_gate_up, act)):
             ops.gemm_tc_silu(x, self.w_gate_up, act)                  # product + SiLU·mul

@@ -50,9 +50,15 @@ class RMSNorm(Part):
                         write_h=write_h and rows is None and delta is not None)
         return out
 
-    def add_into(self, h, y):
-        """``h += norm(y)``: ``y`` [T, H] in float32 or bfloat16, ``h`` the residual stream."""
-        ops.rmsnorm_add(h, y, self.weight, self.eps)
+    def add_into(self, h, y, emit: bool = False):
+        """``h += norm(y)``: ``y`` [T, H] in float32 or bfloat16, ``h`` the residual stream.
+        With ``emit`` (and a compute type other than float32) the new rows are also returned in
+        the compute type, for the sublayer that reads the stream next."""
+        x = None
+        if emit and self.dtype == torch.bfloat16:
+            x = torch.empty(h.shape, dtype=self.dtype, device=h.device)
+        ops.rmsnorm_add(h, y, self.weight, self.eps, x_out=x)
+        return x
 
     def weight_bytes(self):
         return self.weight.numel() * 4
