@@ -78,11 +78,13 @@ def _check_mixer(i: int, kind: str, m: Dict[str, Any]) -> None:
         if heads % g:
             raise ConfigError(f"{where}: heads ({heads}) must be a multiple of kv_heads ({g})")
     if kind in ("attention", "latent_attention"):
-        if not isinstance(m.get("mask"), dict):
-            raise ConfigError(f"{where}: mask.size (the window) is missing")
-        _positive_int(where + ".mask", m["mask"], "size")
-        if not isinstance(m.get("scale"), (int, float)) or isinstance(m.get("scale"), bool):
-            raise ConfigError(f"{where}: scale must be a number, got {m.get('scale')!r}")
+        if m.get("mask") is not None:               # no mask: every earlier key is seen
+            if not isinstance(m["mask"], dict):
+                raise ConfigError(f"{where}: mask must be an object with a size")
+            _positive_int(where + ".mask", m["mask"], "size")
+        if m.get("scale") is not None and (not isinstance(m["scale"], (int, float))
+                                           or isinstance(m["scale"], bool) or not m["scale"] > 0):
+            raise ConfigError(f"{where}: scale must be a positive number, got {m['scale']!r}")
     if kind == "attention" and m["vdim"] != m["dim"]:
         raise ConfigError(f"{where}: the values of this mixer are its keys, so vdim "
                           f"({m['vdim']}) must equal dim ({m['dim']})")
@@ -135,6 +137,11 @@ def rigozen_config_from_dict(raw: Dict[str, Any]) -> RigozenConfig:
 
 
 def _mixer_spec(kind: str, m: Dict[str, Any], eps: float) -> PartSpec:
+    if kind != "delta":
+        m = dict(m)
+        m["mask"] = {"size": (m.get("mask") or {}).get("size", 0)}       # 0: all keys
+        if m.get("scale") is None:
+            m["scale"] = m["dim"] ** -0.5
     if kind == "attention":
         return PartSpec("attention", {
             "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],

@@ -1,9 +1,9 @@
 // Causal grouped-query attention over the block cache, one CTA per (token, query head).
 //
 // The plain attention kernel: it serves prefill and decode alike, in 32-bit and in
-// bfloat16 storage, for any number of heads and groups, head sizes in steps of 8 up to
-// 512, an optional sliding window and an optional per-head sink in the softmax's denominator, and it is the kernel the faster ones are checked
-// against.  Maths as in the reference: s = (q·k)·scale with the scale applied after the
+// bfloat16 storage, for any number of heads and groups, any head size up to 512 (16-byte
+// loads where it is a multiple of 8), an optional sliding window and an optional per-head sink
+// in the softmax's denominator, and it is the kernel the faster ones are checked against.  Maths as in the reference: s = (q·k)·scale with the scale applied after the
 // dot (src/attention.cu:690-692), keys after the query's position are masked (:60-77),
 // softmax with running maximum and sum in 32-bit as in the reference's decode kernel
 // (:451-493), query head h reads key/value head h / (heads / kv_heads) (:421-422).
@@ -62,12 +62,16 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
       row = ((unsigned long long)blk * nkv + kvh) * bt + (key % bt);
       const T* kp = kc + row * hd;
       float dot = 0.f;
+      if ((hd & 7) == 0) {
 #pragma unroll 4
-      for (int d = 0; d < hd; d += 8) {
-        float kv[8];
-        load8(kp + d, kv);
+        for (int d = 0; d < hd; d += 8) {
+          float kv[8];
+          load8(kp + d, kv);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+          for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+        }
+      } else {                        // a head size that is no multiple of 8: element by element
+        for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kp[d]), dot);
       }
       s = dot * scale;
     }
@@ -166,7 +170,7 @@ extern "C" int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int 
                                 int nh, int nkv, int hd, float scale, int window, int bt, int T,
                                 const float* sink, void* stream) {
   if (T <= 0) return kOk;
-  if (nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hd % 8 || hd > kMaxHd || bt <= 0 ||
+  if (nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hd > kMaxHd || bt <= 0 ||
       window < 0)
     return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;

@@ -196,7 +196,13 @@ delta_recurrence_kernel(const float* __restrict__ prep, int ldp, float* __restri
       const float4* k4 = reinterpret_cast<const float4*>(ks + tt * dpad + part * kSlice);
       const float4* q4 = reinterpret_cast<const float4*>(qs + tt * dpad + part * kSlice);
       const float g = gs[tt];
+      // The decay first, on every row the lane holds (independent multiplies), then the
+      // products with the key in four chains, then -- once u is known -- the rank-one update
+      // on every row and only then the read-out's chains: each group is a run of independent
+      // instructions, so a lone warp on a scheduler does not wait four cycles for every one.
       float kreg[kKeepK ? DREG : 4];
+#pragma unroll
+      for (int x = 0; x < DREG; ++x) S[x] *= g;
       float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
       for (int x = 0; x < DREG; x += 4) {
@@ -209,18 +215,21 @@ delta_recurrence_kernel(const float* __restrict__ prep, int ldp, float* __restri
       }
       float r = (r0 + r1) + (r2 + r3);
       for (int o = P >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-      const float u = bs[tt] * ((active ? vs[tt * ecols + jl] : 0.f) - g * r);
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      const float u = bs[tt] * ((active ? vs[tt * ecols + jl] : 0.f) - r);
 #pragma unroll
       for (int x = 0; x < DREG; x += 4) {
         float4 kv;
         if (kKeepK) kv = make_float4(kreg[x], kreg[x + 1], kreg[x + 2], kreg[x + 3]);
         else kv = k4[x >> 2];
+        S[x] = fmaf(kv.x, u, S[x]);
+        S[x + 1] = fmaf(kv.y, u, S[x + 1]);
+        S[x + 2] = fmaf(kv.z, u, S[x + 2]);
+        S[x + 3] = fmaf(kv.w, u, S[x + 3]);
+      }
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int x = 0; x < DREG; x += 4) {
         const float4 qv = q4[x >> 2];
-        S[x] = fmaf(kv.x, u, g * S[x]);
-        S[x + 1] = fmaf(kv.y, u, g * S[x + 1]);
-        S[x + 2] = fmaf(kv.z, u, g * S[x + 2]);
-        S[x + 3] = fmaf(kv.w, u, g * S[x + 3]);
         a0 = fmaf(S[x], qv.x, a0);
         a1 = fmaf(S[x + 1], qv.y, a1);
         a2 = fmaf(S[x + 2], qv.z, a2);

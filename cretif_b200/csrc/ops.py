@@ -358,8 +358,8 @@ def attn_simt(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: i
     if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
             or not vc.is_contiguous()):
         raise KernelError("attention: cache must be contiguous [blocks, kv_heads, block, head_dim]")
-    if hd % 8 or hd > 512:
-        raise KernelError(f"attention: head_dim {hd} is not a multiple of 8 up to 512")
+    if hd <= 0 or hd > 512:
+        raise KernelError(f"attention: head_dim {hd} is not in [1, 512]")
     if sink is not None:
         _need(sink, "sink", torch.float32, 1)
         if sink.numel() != nh or not sink.is_contiguous():

@@ -97,9 +97,9 @@ class Attention(Part):
         self.window = int(params.get("window", 0))
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
             raise ValueError(f"attention: {self.nh} heads cannot share {self.nkv} key/value heads")
-        if self.hd % 8 or not 8 <= self.hd <= 512:
-            raise ValueError(f"attention: head_dim {self.hd} is not a multiple of 8 in [8, 512]; "
-                             "the attention kernels take no other head size")
+        if not 1 <= self.hd <= 512:
+            raise ValueError(f"attention: head_dim {self.hd} is not in [1, 512]; the attention "
+                             "kernels take no other head size")
         pos = dict(params.get("position") or {"kind": "none"})
         self.position = build_part("position", PartSpec(pos.pop("kind"), pos), hidden_size,
                                    dtype, device)

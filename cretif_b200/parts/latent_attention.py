@@ -44,9 +44,9 @@ class LatentAttention(Part):
         self.eps = float(params["eps"])
         if min(self.nh, self.hd, self.vd, self.rank) <= 0:
             raise ValueError("latent_attention: sizes must be positive")
-        if self.rank % 8 or self.rank > 512:
-            raise ValueError(f"latent_attention: latent_rank {self.rank} is not a multiple of 8 up "
-                             "to 512; the attention kernels take no other size")
+        if self.rank > 512:
+            raise ValueError(f"latent_attention: latent_rank {self.rank} is above 512; the "
+                             "attention kernels take no larger head")
         self.sink = None
 
     @classmethod

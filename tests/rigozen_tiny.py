@@ -51,8 +51,18 @@ R_C = {
         {"type": "latent_attention", "mixer": _lat(1, 8, 16, 8, 2, 0.5), "mlp": None},
     ],
 }
-CONFIGS = {"A": R_A, "B": R_B, "C": R_C}
-SEEDS = {"A": 101, "B": 202, "C": 303}
+# sizes that are multiples of nothing in particular: head sizes 12 and 20, a latent of 20, an
+# odd vocabulary, a width of 40; a window longer than any test sequence
+R_D = {
+    "architecture": "Rigozen", "vocab": 77, "width": 40, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "attention", "mixer": _att(3, 1, 12, 500, 0.29), "mlp": _ff(56)},
+        {"type": "delta", "mixer": _delta(3, 1, 12, 6, 5), "mlp": None},
+        {"type": "latent_attention", "mixer": _lat(2, 20, 6, 20, 5, 0.3), "mlp": _ff(24)},
+    ],
+}
+CONFIGS = {"A": R_A, "B": R_B, "C": R_C, "D": R_D}
+SEEDS = {"A": 101, "B": 202, "C": 303, "D": 404}
 
 
 def one_layer(kind: str, window: int = 12):

@@ -41,7 +41,7 @@ def test_config_to_spec_and_manifest(tmp_path):
 @pytest.mark.parametrize("edit,text", [
     (lambda c: c["layers"][0].update(type="conv"), "type"),
     (lambda c: c["layers"][1]["mixer"].update(vdim=8), "vdim"),
-    (lambda c: c["layers"][1]["mixer"].pop("mask"), "mask"),
+    (lambda c: c["layers"][1]["mixer"].update(mask=7), "mask"),
     (lambda c: c["layers"][0]["mixer"].update(kv_heads=3), "kv_heads"),
     (lambda c: c["layers"][3].update(weights_of=3), "weights_of"),
     (lambda c: c["layers"][3].update(weights_of=0), "another layer"),
@@ -54,6 +54,16 @@ def test_bad_configurations_are_refused(edit, text):
     edit(cfg)
     with pytest.raises(ConfigError, match=text):
         rigozen_config_from_dict(cfg)
+
+
+def test_a_mixer_without_mask_or_scale_sees_every_key_at_the_usual_scale():
+    from cretif_b200.config import build_rigozen_spec, rigozen_config_from_dict
+    cfg = copy.deepcopy(tiny.R_A)
+    del cfg["layers"][1]["mixer"]["mask"], cfg["layers"][1]["mixer"]["scale"]
+    del cfg["layers"][3]["mixer"]["mask"], cfg["layers"][3]["mixer"]["scale"]
+    spec = build_rigozen_spec(rigozen_config_from_dict(cfg))
+    params = spec.layers[1].branches[0].part.params
+    assert params["window"] == 0 and params["scale"] == 16 ** -0.5
 
 
 def test_plain_delta_rule_recalls_what_it_stored():

@@ -34,7 +34,8 @@ def close(got, want, dtype):
     return per_row.mean() <= TOL[dtype] and per_row.max() <= BF16_WORST
 
 
-LENGTHS = {"A": [1, 2, 3, 10, 23, 75, 140], "B": [1, 5, 64, 65, 131, 200], "C": [1, 2, 9, 40]}
+LENGTHS = {"A": [1, 2, 3, 10, 23, 75, 140], "B": [1, 5, 64, 65, 131, 200], "C": [1, 2, 9, 40],
+           "D": [1, 4, 31, 70, 100]}
 
 
 def _write(tmp_path_factory, name, cfg, seed, edit=None):
@@ -267,7 +268,8 @@ def test_fast_attention_kernels_with_a_sink(H, G, d, window):
 
 
 @pytest.mark.parametrize("H,G,d,e,taps", [(4, 2, 16, 24, 3), (2, 2, 32, 32, 4), (1, 1, 8, 8, 1),
-                                          (3, 1, 40, 12, 2), (2, 1, 128, 64, 4), (1, 1, 72, 130, 2)])
+                                          (3, 1, 40, 12, 2), (2, 1, 128, 64, 4), (1, 1, 72, 130, 2),
+                                          (1, 1, 256, 32, 2)])
 def test_delta_rule_kernels_in_pieces(H, G, d, e, taps):
     """Convolution, gates and recurrence over a sequence fed in pieces of 1 to 40 tokens into
     a slot's state, against the recurrence written out token by token."""
@@ -342,7 +344,7 @@ def test_one_layer_of_each_mixer(tmp_path_factory, kind, dtype):
 
 # ------------------------------------------------------------------ ways of cutting the work
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole_and_token_by_token(engines, plain_logits, name, dtype):
     eng = engines(name, dtype)
     for n in LENGTHS[name]:
@@ -370,7 +372,7 @@ def test_portions_of_a_prompt(engines, plain_logits, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_unequal_batches_against_each_alone_and_reused_slots(engines, plain_logits, name, dtype):
     """Batches of unequal requests on a cache too small for two batches: the second and third
     rounds get slots, blocks and states that were used before."""
