@@ -116,6 +116,10 @@ __global__ void delta_conv_state_kernel(const float* __restrict__ proj, int ldp,
 
 constexpr int kChunk = 16;
 
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   const unsigned a = (unsigned)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(src) : "memory");
@@ -127,7 +131,7 @@ delta_recurrence_kernel(const float* __restrict__ prep, int ldp, float* __restri
                         size_t state_stride,
                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                         int H, int G, int d, int e, int P, int ecols, float* __restrict__ o_raw,
-                        int write_state) {
+                        int write_state, int vec) {
   extern __shared__ __align__(16) float sm[];
   // with at most 512 threads a lane also keeps the token's key slice in registers between
   // the two passes over its rows
@@ -146,11 +150,13 @@ delta_recurrence_kernel(const float* __restrict__ prep, int ldp, float* __restri
   const int tid = threadIdx.x, part = tid % P, jl = tid / P, j = col0 + jl;
   const bool active = jl < ecols;
   float* M = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e;
-  float S[DREG];
+  // the lane's rows in pairs: the arithmetic below is two-wide (one instruction, two rows)
+  float2 S[DREG / 2];
 #pragma unroll
-  for (int r = 0; r < DREG; ++r) {
-    const int i = part * DREG + r;
-    S[r] = (active && i < d) ? M[(size_t)i * e + j] : 0.f;
+  for (int r = 0; r < DREG / 2; ++r) {
+    const int i = part * DREG + 2 * r;
+    S[r].x = (active && i < d) ? M[(size_t)i * e + j] : 0.f;
+    S[r].y = (active && i + 1 < d) ? M[(size_t)(i + 1) * e + j] : 0.f;
   }
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
   const int C = 2 * G * d + H * e;
@@ -163,16 +169,34 @@ delta_recurrence_kernel(const float* __restrict__ prep, int ldp, float* __restri
     float* vs = ks + kChunk * dpad;
     float* bs = vs + kChunk * ecols;
     const int n = min(kChunk, t1 - c0);
-    for (int idx = tid; idx < n * d; idx += blockDim.x) {
-      const int tt = idx / d, i = idx - tt * d;
-      const int at = tt * dpad + (i / DREG) * kSlice + (i % DREG);
-      const float* row = prep + (size_t)(c0 + tt) * ldp;
-      cp_async4(qs + at, row + (size_t)grp * d + i);
-      cp_async4(ks + at, row + (size_t)(G + grp) * d + i);
-    }
-    for (int idx = tid; idx < n * ecols; idx += blockDim.x) {
-      const int tt = idx / ecols, i = idx - tt * ecols;
-      cp_async4(vs + idx, prep + (size_t)(c0 + tt) * ldp + 2 * G * d + (size_t)h * e + col0 + i);
+    if (vec) {
+      // 16 bytes a copy: a warp's copy instruction moves 512 bytes (a lone 2,048-token prompt
+      // at 16 heads of 128 x 128: 1.40 -> 1.27 ms a layer against 4-byte copies)
+      const int d4 = d >> 2, e4 = ecols >> 2;
+      for (int idx = tid; idx < n * d4; idx += blockDim.x) {
+        const int tt = idx / d4, i = (idx - tt * d4) << 2;
+        const int at = tt * dpad + (i / DREG) * kSlice + (i % DREG);
+        const float* row = prep + (size_t)(c0 + tt) * ldp;
+        cp_async16(qs + at, row + (size_t)grp * d + i);
+        cp_async16(ks + at, row + (size_t)(G + grp) * d + i);
+      }
+      for (int idx = tid; idx < n * e4; idx += blockDim.x) {
+        const int tt = idx / e4, i = (idx - tt * e4) << 2;
+        cp_async16(vs + tt * ecols + i,
+                   prep + (size_t)(c0 + tt) * ldp + 2 * G * d + (size_t)h * e + col0 + i);
+      }
+    } else {
+      for (int idx = tid; idx < n * d; idx += blockDim.x) {
+        const int tt = idx / d, i = idx - tt * d;
+        const int at = tt * dpad + (i / DREG) * kSlice + (i % DREG);
+        const float* row = prep + (size_t)(c0 + tt) * ldp;
+        cp_async4(qs + at, row + (size_t)grp * d + i);
+        cp_async4(ks + at, row + (size_t)(G + grp) * d + i);
+      }
+      for (int idx = tid; idx < n * ecols; idx += blockDim.x) {
+        const int tt = idx / ecols, i = idx - tt * ecols;
+        cp_async4(vs + idx, prep + (size_t)(c0 + tt) * ldp + 2 * G * d + (size_t)h * e + col0 + i);
+      }
     }
     if (tid < n) {
       cp_async4(bs + tid, prep + (size_t)(c0 + tid) * ldp + C + h);
@@ -192,59 +216,64 @@ delta_recurrence_kernel(const float* __restrict__ prep, int ldp, float* __restri
     const float* vs = ks + kChunk * dpad;
     const float* bs = vs + kChunk * ecols;
     const float* gs = bs + kChunk;
+    // the token's three scalars are read a token ahead
+    float g_next = gs[0], b_next = bs[0], v_next = active ? vs[jl] : 0.f;
+    float* orow = o_raw + (size_t)c0 * H * e + (size_t)h * e + j;
     for (int tt = 0; tt < n; ++tt) {
       const float4* k4 = reinterpret_cast<const float4*>(ks + tt * dpad + part * kSlice);
       const float4* q4 = reinterpret_cast<const float4*>(qs + tt * dpad + part * kSlice);
-      const float g = gs[tt];
+      const float g = g_next, beta = b_next, vj = v_next;
+      if (tt + 1 < n) {
+        g_next = gs[tt + 1];
+        b_next = bs[tt + 1];
+        v_next = active ? vs[(tt + 1) * ecols + jl] : 0.f;
+      }
       // The decay first, on every row the lane holds (independent multiplies), then the
       // products with the key in four chains, then -- once u is known -- the rank-one update
       // on every row and only then the read-out's chains: each group is a run of independent
       // instructions, so a lone warp on a scheduler does not wait four cycles for every one.
-      float kreg[kKeepK ? DREG : 4];
+      // All of it two rows an instruction (fma.f32x2).
+      float4 kreg[kKeepK ? DREG / 4 : 1];
+      const float2 g2 = make_float2(g, g);
 #pragma unroll
-      for (int x = 0; x < DREG; ++x) S[x] *= g;
-      float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+      for (int x = 0; x < DREG / 2; ++x) S[x] = __fmul2_rn(S[x], g2);
+      float2 ra = make_float2(0.f, 0.f), rb = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int x = 0; x < DREG; x += 4) {
-        const float4 kv = k4[x >> 2];
-        if (kKeepK) { kreg[x] = kv.x; kreg[x + 1] = kv.y; kreg[x + 2] = kv.z; kreg[x + 3] = kv.w; }
-        r0 = fmaf(S[x], kv.x, r0);
-        r1 = fmaf(S[x + 1], kv.y, r1);
-        r2 = fmaf(S[x + 2], kv.z, r2);
-        r3 = fmaf(S[x + 3], kv.w, r3);
+      for (int x = 0; x < DREG / 4; ++x) {
+        const float4 kv = k4[x];
+        if (kKeepK) kreg[x] = kv;
+        ra = __ffma2_rn(S[2 * x], make_float2(kv.x, kv.y), ra);
+        rb = __ffma2_rn(S[2 * x + 1], make_float2(kv.z, kv.w), rb);
       }
-      float r = (r0 + r1) + (r2 + r3);
+      float r = (ra.x + ra.y) + (rb.x + rb.y);
       for (int o = P >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-      const float u = bs[tt] * ((active ? vs[tt * ecols + jl] : 0.f) - r);
+      const float u = beta * (vj - r);
+      const float2 u2 = make_float2(u, u);
 #pragma unroll
-      for (int x = 0; x < DREG; x += 4) {
-        float4 kv;
-        if (kKeepK) kv = make_float4(kreg[x], kreg[x + 1], kreg[x + 2], kreg[x + 3]);
-        else kv = k4[x >> 2];
-        S[x] = fmaf(kv.x, u, S[x]);
-        S[x + 1] = fmaf(kv.y, u, S[x + 1]);
-        S[x + 2] = fmaf(kv.z, u, S[x + 2]);
-        S[x + 3] = fmaf(kv.w, u, S[x + 3]);
+      for (int x = 0; x < DREG / 4; ++x) {
+        const float4 kv = kKeepK ? kreg[x] : k4[x];
+        S[2 * x] = __ffma2_rn(make_float2(kv.x, kv.y), u2, S[2 * x]);
+        S[2 * x + 1] = __ffma2_rn(make_float2(kv.z, kv.w), u2, S[2 * x + 1]);
       }
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      float2 aa = make_float2(0.f, 0.f), ab = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int x = 0; x < DREG; x += 4) {
-        const float4 qv = q4[x >> 2];
-        a0 = fmaf(S[x], qv.x, a0);
-        a1 = fmaf(S[x + 1], qv.y, a1);
-        a2 = fmaf(S[x + 2], qv.z, a2);
-        a3 = fmaf(S[x + 3], qv.w, a3);
+      for (int x = 0; x < DREG / 4; ++x) {
+        const float4 qv = q4[x];
+        aa = __ffma2_rn(S[2 * x], make_float2(qv.x, qv.y), aa);
+        ab = __ffma2_rn(S[2 * x + 1], make_float2(qv.z, qv.w), ab);
       }
+      const float a0 = aa.x, a1 = aa.y, a2 = ab.x, a3 = ab.y;
       float acc = (a0 + a1) + (a2 + a3);
       for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (active && part == 0) o_raw[(size_t)(c0 + tt) * H * e + (size_t)h * e + j] = acc;
+      if (active && part == 0) orow[(size_t)tt * H * e] = acc;
     }
   }
   if (write_state) {
 #pragma unroll
-    for (int r = 0; r < DREG; ++r) {
-      const int i = part * DREG + r;
-      if (active && i < d) M[(size_t)i * e + j] = S[r];
+    for (int r = 0; r < DREG / 2; ++r) {
+      const int i = part * DREG + 2 * r;
+      if (active && i < d) M[(size_t)i * e + j] = S[r].x;
+      if (active && i + 1 < d) M[(size_t)(i + 1) * e + j] = S[r].y;
     }
   }
 }
@@ -287,8 +316,11 @@ static int launch_recurrence_t(const float* prep, int ldp, float* state, size_t 
                                            (int)smem);
     if (err != cudaSuccess) return (int)err;
   }
+  // 16-byte copies of a chunk's operands where every address they touch is 16-byte aligned
+  const int vec = ldp % 4 == 0 && d % 4 == 0 && e % 4 == 0 && ecols % 4 == 0 &&
+                  ((uintptr_t)prep & 15) == 0;
   kern<<<dim3(B, H, e / ecols), threads, smem, st>>>(prep, ldp, state, state_stride, cu, seq_slot,
-                                                     H, G, d, e, P, ecols, o_raw, write_state);
+                                                     H, G, d, e, P, ecols, o_raw, write_state, vec);
   return launch_status();
 }
 
