@@ -37,6 +37,7 @@ class KVRequest:
     head_dim: int
     window: int = 0          # 0: every key is kept; W > 0: the last W keys
     shared_values: bool = False   # one tensor serves as keys and values (a cached latent)
+    value_dim: int = 0       # size of a value head when it is not head_dim
 
 
 @dataclass(frozen=True)
@@ -56,6 +57,12 @@ class KVView:
     window: int
 
 
+def _id_order(cid):
+    """Cache ids are integers or tuples of integers and names; any mixture sorts."""
+    return tuple((0, x) if isinstance(x, int) else (1, str(x))
+                 for x in (cid if isinstance(cid, tuple) else (cid,)))
+
+
 class _KVGroup:
     def __init__(self, request: KVRequest, cache_ids: List[int], n_blocks: int,
                  block_tokens: int, max_slots: int, blocks_per_seq: int, dtype, device):
@@ -65,7 +72,10 @@ class _KVGroup:
         self.blocks_per_seq = blocks_per_seq
         shape = (len(cache_ids), n_blocks, request.num_kv_heads, block_tokens, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = self.k if request.shared_values else torch.zeros(shape, dtype=dtype,
+        if request.shared_values and request.value_dim not in (0, request.head_dim):
+            raise ValueError("keys that serve as values have the values' size")
+        vshape = shape[:-1] + (request.value_dim or request.head_dim,)
+        self.v = self.k if request.shared_values else torch.zeros(vshape, dtype=dtype,
                                                                   device=device)
         self.pool = BlockPool(n_blocks)
         self.table_host = np.full((max_slots, blocks_per_seq), -1, dtype=np.int32)
@@ -162,17 +172,23 @@ class SequenceCache:
         self._kv_of: Dict[int, Tuple[_KVGroup, int]] = {}
         self._state: Dict[int, torch.Tensor] = {}
         by_request: Dict[KVRequest, List[int]] = {}
-        for cid in sorted(requests):
-            req = requests[cid]
-            if req is None:
-                continue
-            if isinstance(req, KVRequest):
-                by_request.setdefault(req, []).append(cid)
-            elif isinstance(req, StateRequest):
-                self._state[cid] = torch.zeros((self.max_slots, *req.shape), dtype=req.dtype,
-                                               device=self.device)
-            else:
-                raise TypeError(f"cache id {cid}: unknown cache request {req!r}")
+        for cid in sorted(requests, key=_id_order):
+            # a part may ask for both kinds at once (keys and values, and a state beside them)
+            reqs = requests[cid]
+            reqs = list(reqs) if isinstance(reqs, (tuple, list)) else [reqs]
+            kinds = [type(r) for r in reqs if r is not None]
+            if len(kinds) != len(set(kinds)):
+                raise TypeError(f"cache id {cid}: two requests of one kind")
+            for req in reqs:
+                if req is None:
+                    continue
+                if isinstance(req, KVRequest):
+                    by_request.setdefault(req, []).append(cid)
+                elif isinstance(req, StateRequest):
+                    self._state[cid] = torch.zeros((self.max_slots, *req.shape), dtype=req.dtype,
+                                                   device=self.device)
+                else:
+                    raise TypeError(f"cache id {cid}: unknown cache request {req!r}")
         for req, cids in by_request.items():
             g = _KVGroup(req, cids, self.n_blocks, block_tokens, self.max_slots,
                          self.blocks_per_seq, dtype, self.device)
@@ -286,7 +302,7 @@ class SequenceCache:
 
     # -- accounting ----------------------------------------------------------------
     def stats(self) -> dict:
-        kv_bytes = sum(g.k.numel() * g.k.element_size() * (1 if g.v is g.k else 2)
+        kv_bytes = sum((g.k.numel() + (0 if g.v is g.k else g.v.numel())) * g.k.element_size()
                        for g in self._kv_groups)
         state_bytes = sum(t.numel() * t.element_size() for t in self._state.values())
         return {
@@ -298,6 +314,7 @@ class SequenceCache:
             "kv_bytes": kv_bytes,
             "state_bytes": state_bytes,
             "groups": [{"num_kv_heads": g.request.num_kv_heads, "head_dim": g.request.head_dim,
+                        "value_dim": g.request.value_dim or g.request.head_dim,
                         "window": g.request.window, "layers": len(g.cache_ids)}
                        for g in self._kv_groups],
         }

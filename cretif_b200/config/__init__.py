@@ -4,6 +4,7 @@ from .registry import (ConfigError, architecture_name, load_config, read_config_
 from .spec import BranchSpec, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, prenorm_layer
 from .llama import LlamaConfig, build_llama_spec, llama_config_from_dict
 from .rigozen import RigozenConfig, build_rigozen_spec, rigozen_config_from_dict
+from .losorax import LosoraxConfig, build_losorax_spec, losorax_config_from_dict
 from .presets import PRESETS, preset
 
 __all__ = [
@@ -12,4 +13,5 @@ __all__ = [
     "BranchSpec", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "prenorm_layer",
     "LlamaConfig", "build_llama_spec", "llama_config_from_dict", "PRESETS", "preset",
     "RigozenConfig", "build_rigozen_spec", "rigozen_config_from_dict",
+    "LosoraxConfig", "build_losorax_spec", "losorax_config_from_dict",
 ]

@@ -30,16 +30,19 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class BranchSpec:
-    """One residual branch of a block: ``h += post_norm(part(norm(h)))``.
+    """One residual branch of a block: ``h += post_norm(part(shift(norm(h))))``.
 
     ``role`` is the part's category (``"mixer"`` or ``"feed_forward"``); ``norm`` stands
-    before the part and ``post_norm`` after it, and either may be absent.
+    before the part and ``post_norm`` after it, and either may be absent.  ``shift`` (a part
+    of the ``shift`` category, optional) stands between the norm and the part: it blends each
+    token's row with the row of the token before it and keeps a row per sequence between steps.
     """
 
     role: str
     part: PartSpec
     norm: Optional[PartSpec] = None
     post_norm: Optional[PartSpec] = None
+    shift: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -76,7 +79,9 @@ class ScheduleEntry:
     ``layer`` indexes ``ModelSpec.layers``; the same layer may be visited twice
     (its weights are shared).  ``cache`` names the cache the visit's mixer uses:
     ``None`` gives the visit a cache of its own; an integer ``j`` lets it read
-    the cache that schedule entry ``j`` (an earlier one) writes, without writing.
+    the keys and values that schedule entry ``j`` (an earlier one) writes, without
+    writing.  What a visit's parts keep per sequence in fixed size (a recurrent state,
+    the last inputs of a convolution, a shifted row) is always the visit's own.
     """
 
     layer: int

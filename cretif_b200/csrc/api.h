@@ -70,6 +70,61 @@ int cretif_delta_recurrence(const float* prep, int ldp, const float* gate, int l
                             float* o_raw, void* out, int out_dt, int ldo, int write_state, int T,
                             void* stream);
 
+// Dynamic Tanh, dyt(x) = (tanh(alpha x) w + b) gain, a norm without statistics (pointwise_norm.cu);
+// alpha points at one float on the device, gain may be null.
+// dyt_rows: v = h[src] (+ delta[src]); if write_h, h[src] = v; out[r] = dyt(v); src = rows ? rows[r] : r.
+int cretif_dyt_rows(float* h, const void* delta, int delta_dt, const float* w, const float* b,
+                    const float* alpha, const float* gain, void* out, int out_dt, const int* rows,
+                    int R, int H, int write_h, void* stream);
+// h[r] += dyt(y[r]): the norm on a sublayer's output, fused with the residual sum.
+int cretif_dyt_add(float* h, const void* y, int y_dt, int ldy, const float* w, const float* b,
+                   const float* alpha, const float* gain, int R, int H, void* stream);
+// out[t] = n[t] + (n[t-1] - n[t]) * shift with n = dyt(h) (n = h when w is null); a sequence's
+// first token of the step reads the row saved in state[slot] and replaces it by the step's last.
+int cretif_shift_rows(const float* h, const float* w, const float* b, const float* alpha,
+                      const float* shift, float* state, long long state_stride,
+                      const int* tok_seq, const int* seq_slot, const int* cu_seqlens, void* out,
+                      int out_dt, int T, int H, void* stream);
+
+// Between an attention's projections and its scores (conv_attn.cu): causal convolution over
+// time of every channel of proj [q (nh hd) | k (nkv hd) | v (nkv vd)] (float32), unit RMS per q
+// and k head, the query times 1 + gain_coef ln(floor((pos + 1) / gain_every) + 1) (gain_every
+// 0: no gain), q into q_out, k and v into the block cache.  nkv = 0: queries only.
+int cretif_conv_headnorm_kv_append(const float* proj, int ldp, const float* conv_w, int taps,
+                                   const float* conv_state, long long state_stride,
+                                   const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                   const int* seq_start, int nh, int nkv, int hd, int vd,
+                                   float eps, float gain_coef, int gain_every, void* q_out,
+                                   int ldq, int dt, const int* table, int table_stride, void* kc,
+                                   void* vc, int bt, int write_cache, int T, unsigned int* fault,
+                                   void* stream);
+
+// The generalized delta rule (delta_rule.cu).  proj rows (float32): [r (H d) | k (H d) | v (H e) |
+// gate (H e) | a (H d) | w1 (R)]; prep rows: [u (H d) | b (H d) | w (H d)].
+int cretif_general_delta_prepare(const float* proj, int ldp, float* prep, int ldo,
+                                 const float* a_bias, const float* w2, const float* w0, int R,
+                                 int H, int d, int e, float unit_eps, float decay_scale, int T,
+                                 void* stream);
+int cretif_general_delta_recurrence(const float* proj, int ldp, const float* prep, int ldq,
+                                    const float* gate, int ldg, float* state,
+                                    long long state_stride, const int* cu_seqlens,
+                                    const int* seq_slot, int B, int H, int d, int e,
+                                    const float* norm_w, int per_head_weight, int gate_sigmoid,
+                                    float eps, float* o_raw, void* out, int out_dt, int ldo,
+                                    int write_state, int T, void* stream);
+
+// Routed experts (moe.cu).
+int cretif_moe_route(const void* x, int x_dt, int ldx, const float* router_w, int E, int H,
+                     int top, int renorm, int* ids, float* wts, int T, void* stream);
+int cretif_moe_group(const int* ids, int P, int E, int* offsets, int* place, int* order,
+                     int* tile_expert, int* tile_row0, int max_tiles, void* stream);
+int cretif_moe_gemm(const void* A, int a_dt, int lda, const void* W, int w_dt, void* C, int ldc,
+                    int N, int K, int top, int mode, int scale_at, const float* wts,
+                    const int* order, const int* offsets, const int* tile_expert,
+                    const int* tile_row0, int max_tiles, int use_mma, void* stream);
+int cretif_moe_combine(const float* rows, int ld, const int* place, int top, float* y, int T,
+                       int H, void* stream);
+
 // After a decode step: ids <- sampled (if given), positions and lengths + 1.
 int cretif_advance_decode(int* tok_ids, int* tok_pos, int* seq_start, const int* sampled, int B,
                           void* stream);
@@ -129,10 +184,14 @@ int cretif_gemm_tc_qkv_rope(const void* A, const void* Wqkv, void* Q, int ldq, c
 
 // Causal grouped-query attention over the block cache, any step shape.  sink (may be null):
 // one float per query head, exp(sink) joins the softmax's denominator without a key or value.
+// vd: size of a value head (the cache's values are [blocks, nkv, bt, vd], out rows nh * vd).
+// bias (may be null): float32 [bias_rows, nh] added to the scaled score of the key n positions
+// back, row = the last r with bias_edges[r] <= n (edges ascending, edges[0] = 0).
 int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int dt, const void* kc,
                      const void* vc, const int* table, int table_stride, const int* tok_pos,
                      const int* tok_seq, const int* seq_slot, int nh, int nkv, int hd, float scale,
-                     int window, int bt, int T, const float* sink, void* stream);
+                     int window, int bt, int T, const float* sink, int vd, const float* bias,
+                     const int* bias_edges, int bias_rows, void* stream);
 
 // Decode attention (one query token per sequence), bfloat16, keys split into n_splits <= 64
 // ranges per (sequence, kv head); part_o/part_ml are float32 scratch of the sizes that

@@ -2,8 +2,9 @@
 //
 // The plain attention kernel: it serves prefill and decode alike, in 32-bit and in
 // bfloat16 storage, for any number of heads and groups, any head size up to 512 (16-byte
-// loads where it is a multiple of 8), an optional sliding window and an optional per-head sink
-// in the softmax's denominator, and it is the kernel the faster ones are checked against.  Maths as in the reference: s = (q·k)·scale with the scale applied after the
+// loads where it is a multiple of 8), a value size of its own, an optional sliding window, an
+// optional per-head sink in the softmax's denominator and an optional learned bias by distance
+// (below), and it is the kernel the faster ones are checked against.  Maths as in the reference: s = (q·k)·scale with the scale applied after the
 // dot (src/attention.cu:690-692), keys after the query's position are masked (:60-77),
 // softmax with running maximum and sum in 32-bit as in the reference's decode kernel
 // (:451-493), query head h reads key/value head h / (heads / kv_heads) (:421-422).
@@ -14,6 +15,11 @@
 // of an eighth the length.  A (token, head) is always reduced in the same order, so its
 // output does not depend on what else is in the batch or on how the tokens were cut into
 // steps.
+//
+// Bias by distance: a table bias[rows, heads] and ascending edges[rows] (edges[0] = 0); a key
+// n = pos - key positions back adds bias[r, h] to its scaled score, where r is the last row
+// with edges[r] <= n.  The host lays the edges out (a row per distance, then rows spaced by the
+// logarithm, or anything else that is monotone); the kernel only searches them.
 #include "api.h"
 #include "common.cuh"
 
@@ -21,6 +27,7 @@ namespace cretif {
 
 constexpr int kWarps = 8;
 constexpr int kMaxHd = 512;
+constexpr int kMaxBiasRows = 1024;
 
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -29,8 +36,12 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
                  const int* __restrict__ table, int table_stride,
                  const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                  const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale,
-                 int window, int bt, int T_tokens, const float* __restrict__ sink) {
+                 int window, int bt, int T_tokens, const float* __restrict__ sink, int vd,
+                 const float* __restrict__ bias, const int* __restrict__ bias_edges,
+                 int bias_rows) {
   __shared__ float qs[kMaxHd];
+  __shared__ float bias_s[kMaxBiasRows];
+  __shared__ int edge_s[kMaxBiasRows];
   __shared__ float part_acc[kWarps][kMaxHd];
   __shared__ float part_m[kWarps], part_l[kWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -44,6 +55,11 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
 
   const T* qrow = q + (size_t)t * ldq + (size_t)h * hd;
   for (int d = threadIdx.x; d < hd; d += kWarps * 32) qs[d] = to_float(qrow[d]);
+  if (bias)
+    for (int r = threadIdx.x; r < bias_rows; r += kWarps * 32) {
+      bias_s[r] = bias[(size_t)r * nh + h];
+      edge_s[r] = bias_edges[r];
+    }
   __syncthreads();
 
   float m = -INFINITY, l = 0.f;
@@ -74,6 +90,16 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
         for (int d = 0; d < hd; ++d) dot = fmaf(qs[d], to_float(kp[d]), dot);
       }
       s = dot * scale;
+      if (bias) {
+        // the last row whose edge is at or below the distance
+        const int n = pos - key;
+        int lo = 0, hi = bias_rows - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (edge_s[mid] <= n) lo = mid; else hi = mid - 1;
+        }
+        s += bias_s[lo];
+      }
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = valid ? expf(s - m_new) : 0.f;
@@ -96,12 +122,12 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
         const float pu = __shfl_sync(0xffffffffu, p, j);
         const unsigned long long ru = __shfl_sync(0xffffffffu, row, j);
         pj[u] = j0 + u < n_valid ? pu : 0.f;
-        vp[u] = vc + ru * hd;
+        vp[u] = vc + ru * vd;
       }
 #pragma unroll
       for (int i = 0; i < kMaxHd / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) {
+        if (d < vd) {
           float v[kAhead];
 #pragma unroll
           for (int u = 0; u < kAhead; ++u) v[u] = pj[u] != 0.f ? to_float(vp[u][d]) : 0.f;
@@ -120,7 +146,7 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
 #pragma unroll
   for (int i = 0; i < kMaxHd / 32; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) part_acc[warp][d] = acc[i];
+    if (d < vd) part_acc[warp][d] = acc[i];
   }
   __syncthreads();
   if (warp != 0) return;
@@ -139,7 +165,7 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
 #pragma unroll
     for (int i = 0; i < kMaxHd / 32; ++i) {
       const int d = lane + 32 * i;
-      if (d < hd) acc[i] = fmaf(part_acc[w][d], a, acc[i]);
+      if (d < vd) acc[i] = fmaf(part_acc[w][d], a, acc[i]);
     }
   }
   if (sink) {
@@ -152,11 +178,11 @@ attn_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
     for (int i = 0; i < kMaxHd / 32; ++i) acc[i] *= a;
   }
   const float inv = 1.0f / l_all;
-  T* orow = out + (size_t)t * ldo + (size_t)h * hd;
+  T* orow = out + (size_t)t * ldo + (size_t)h * vd;
 #pragma unroll
   for (int i = 0; i < kMaxHd / 32; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) orow[d] = from_float<T>(acc[i] * inv);
+    if (d < vd) orow[d] = from_float<T>(acc[i] * inv);
   }
 }
 
@@ -168,11 +194,13 @@ extern "C" int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int 
                                 const void* vc, const int* table, int table_stride,
                                 const int* tok_pos, const int* tok_seq, const int* seq_slot,
                                 int nh, int nkv, int hd, float scale, int window, int bt, int T,
-                                const float* sink, void* stream) {
+                                const float* sink, int vd, const float* bias,
+                                const int* bias_edges, int bias_rows, void* stream) {
   if (T <= 0) return kOk;
   if (nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hd > kMaxHd || bt <= 0 ||
-      window < 0)
+      window < 0 || vd <= 0 || vd > kMaxHd)
     return kBadArgument;
+  if (bias && (!bias_edges || bias_rows <= 0 || bias_rows > kMaxBiasRows)) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
   const long long items = (long long)T * nh;
   if (items > 0x7fffffffLL) return kBadArgument;
@@ -180,12 +208,13 @@ extern "C" int cretif_attn_simt(const void* q, int ldq, void* out, int ldo, int 
   if (dt == kF32)
     attn_simt_kernel<float><<<blocks, kWarps * 32, 0, st>>>(
         (const float*)q, ldq, (float*)out, ldo, (const float*)kc, (const float*)vc, table,
-        table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd, scale, window, bt, T, sink);
+        table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd, scale, window, bt, T, sink, vd, bias,
+        bias_edges, bias_rows);
   else if (dt == kBF16)
     attn_simt_kernel<__nv_bfloat16><<<blocks, kWarps * 32, 0, st>>>(
         (const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)kc,
         (const __nv_bfloat16*)vc, table, table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, hd,
-        scale, window, bt, T, sink);
+        scale, window, bt, T, sink, vd, bias, bias_edges, bias_rows);
   else
     return kBadDType;
   return launch_status();

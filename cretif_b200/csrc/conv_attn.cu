@@ -1,0 +1,133 @@
+// What stands between an attention's projections and its scores when the projections pass a
+// short causal convolution over time: convolution, unit length per head, a gain on the query
+// that grows with the position, and the write into the block cache -- one kernel, 32-bit.
+//
+// proj rows (float32): [q (nh hd) | k (nkv hd) | v (nkv vd)]; a layer that reads another layer's
+// keys and values has only the q columns (nkv = 0 here).  Channel c of a row is convolved with
+// taps weights conv_w[c, :] (the last one for the present token) over this step's earlier rows of
+// the same sequence and, where the window reaches back before the step, over the sequence's saved
+// last taps-1 inputs (conv_state, [C, taps-1] per slot, zeros at a sequence's start).  Then
+//   q head:  x / sqrt(mean(x^2) + eps) * (1 + coef * ln(floor((pos + 1) / every) + 1))  -> q_out
+//   k head:  x / sqrt(mean(x^2) + eps)                                                  -> key cache
+//   v head:  x                                                                          -> value cache
+// A warp per head of a token; a head's channels stay in the lanes' registers between the
+// convolution and the scaling (head sizes up to 512).  The saved inputs are brought up to date
+// afterwards by delta_conv_state (delta_rule.cu), which is the same for every convolved mixer.
+#include "api.h"
+#include "common.cuh"
+
+namespace cretif {
+
+namespace {
+constexpr int kCvWarps = 8;
+constexpr int kCvMaxD = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(kCvWarps * 32)
+conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
+                               const float* __restrict__ conv_w, int taps,
+                               const float* __restrict__ conv_state, size_t state_stride,
+                               const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                               const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                               int nh, int nkv, int hd, int vd, float eps, float gain_coef,
+                               int gain_every, T* __restrict__ q_out, int ldq,
+                               const int* __restrict__ table, int table_stride,
+                               T* __restrict__ kc, T* __restrict__ vc, int bt, int write_cache,
+                               unsigned int* __restrict__ fault) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int unit = blockIdx.y * kCvWarps + warp;
+  if (unit >= nh + 2 * nkv) return;
+  const int b = tok_seq[t];
+  const int pos = tok_pos[t];
+  const int lt = pos - seq_start[b];             // tokens of this sequence before t in the step
+  const int slot = seq_slot[b];
+  const float* st = conv_state + (size_t)slot * state_stride;
+  const float* row = proj + (size_t)t * ldp;
+  auto conv = [&](int c) {
+    float acc = 0.f;
+#pragma unroll 4
+    for (int i = taps - 1; i >= 0; --i) {        // i tokens back, the oldest first
+      const float w = conv_w[(size_t)c * taps + (taps - 1 - i)];
+      const float z = i <= lt ? row[c - (ptrdiff_t)i * ldp]
+                              : st[(size_t)c * (taps - 1) + (taps - 1) - (i - lt)];
+      acc = fmaf(w, z, acc);
+    }
+    return acc;
+  };
+  const bool is_q = unit < nh, is_k = !is_q && unit < nh + nkv;
+  const int n = (is_q || is_k) ? hd : vd;
+  const int c0 = is_q ? unit * hd : is_k ? nh * hd + (unit - nh) * hd
+                                         : (nh + nkv) * hd + (unit - nh - nkv) * vd;
+  float val[kCvMaxD / 32];
+  float ss = 0.f;
+#pragma unroll
+  for (int m = 0; m < kCvMaxD / 32; ++m) {
+    const int i = lane + 32 * m;
+    val[m] = i < n ? conv(c0 + i) : 0.f;
+    ss += val[m] * val[m];
+  }
+  float f = 1.f;
+  if (is_q || is_k) {
+    ss = warp_sum(ss);
+    f = 1.0f / sqrtf(ss / (float)hd + eps);
+  }
+  if (is_q) {
+    if (gain_every > 0) f *= 1.0f + gain_coef * logf((float)((pos + 1) / gain_every + 1));
+    T* q = q_out + (size_t)t * ldq + (size_t)unit * hd;
+#pragma unroll
+    for (int m = 0; m < kCvMaxD / 32; ++m) {
+      const int i = lane + 32 * m;
+      if (i < n) q[i] = from_float<T>(val[m] * f);
+    }
+    return;
+  }
+  if (!write_cache) return;
+  const int blk = table[(size_t)slot * table_stride + pos / bt];
+  if (blk < 0) {
+    if (lane == 0) atomicOr(fault, kFaultBlockTable);
+    return;
+  }
+  const int kvh = is_k ? unit - nh : unit - nh - nkv;
+  T* dst = (is_k ? kc : vc) + (((size_t)blk * nkv + kvh) * bt + (pos % bt)) * n;
+#pragma unroll
+  for (int m = 0; m < kCvMaxD / 32; ++m) {
+    const int i = lane + 32 * m;
+    if (i < n) dst[i] = from_float<T>(val[m] * f);
+  }
+}
+}  // namespace
+}  // namespace cretif
+
+using namespace cretif;
+
+extern "C" int cretif_conv_headnorm_kv_append(
+    const float* proj, int ldp, const float* conv_w, int taps, const float* conv_state,
+    long long state_stride, const int* tok_pos, const int* tok_seq, const int* seq_slot,
+    const int* seq_start, int nh, int nkv, int hd, int vd, float eps, float gain_coef,
+    int gain_every, void* q_out, int ldq, int dt, const int* table, int table_stride, void* kc,
+    void* vc, int bt, int write_cache, int T, unsigned int* fault, void* stream) {
+  if (T <= 0) return kOk;
+  if (nh <= 0 || nkv < 0 || hd <= 0 || hd > kCvMaxD || taps < 1 || ldq < nh * hd)
+    return kBadArgument;
+  if (nkv > 0 && (vd <= 0 || vd > kCvMaxD || bt <= 0 || !kc || !vc || !table)) return kBadArgument;
+  if (ldp < (nh + nkv) * hd + nkv * vd) return kBadArgument;
+  if (taps > 1 && !conv_state) return kBadArgument;
+  const int units = nh + 2 * nkv;
+  dim3 grid(T, (units + kCvWarps - 1) / kCvWarps);
+  if (grid.y > 65535) return kBadArgument;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dt == kF32)
+    conv_headnorm_kv_append_kernel<float><<<grid, kCvWarps * 32, 0, st>>>(
+        proj, ldp, conv_w, taps, conv_state, (size_t)state_stride, tok_pos, tok_seq, seq_slot,
+        seq_start, nh, nkv, hd, vd, eps, gain_coef, gain_every, (float*)q_out, ldq, table,
+        table_stride, (float*)kc, (float*)vc, bt, write_cache, fault);
+  else if (dt == kBF16)
+    conv_headnorm_kv_append_kernel<__nv_bfloat16><<<grid, kCvWarps * 32, 0, st>>>(
+        proj, ldp, conv_w, taps, conv_state, (size_t)state_stride, tok_pos, tok_seq, seq_slot,
+        seq_start, nh, nkv, hd, vd, eps, gain_coef, gain_every, (__nv_bfloat16*)q_out, ldq, table,
+        table_stride, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, bt, write_cache, fault);
+  else
+    return kBadDType;
+  return launch_status();
+}

@@ -283,7 +283,7 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 delta_out_norm_kernel(const float* __restrict__ o_raw, const float* __restrict__ gate, int ldg,
                       const float* __restrict__ norm_w, float eps, TO* __restrict__ out, int ldo,
-                      int H, int e, long long items) {
+                      int H, int e, long long items, int w_stride, int gate_sigmoid) {
   const long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (item >= items) return;
   const int lane = threadIdx.x & 31;
@@ -297,9 +297,15 @@ delta_out_norm_kernel(const float* __restrict__ o_raw, const float* __restrict__
   for (int i = lane; i < e; i += 32) ss += o[i] * o[i];
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)e + eps);
+  // w_stride: 0 when the heads share one weight of e numbers, e when each has its own;
+  // the gate is SiLU or, with gate_sigmoid, the logistic function alone
+  const float* w = norm_w + (size_t)h * w_stride;
 #pragma unroll 4
-  for (int i = lane; i < e; i += 32)
-    orow[i] = from_float<TO>(o[i] * inv * norm_w[i] * silu_f32(grow[i]));
+  for (int i = lane; i < e; i += 32) {
+    const float z = grow[i];
+    const float gate_v = gate_sigmoid ? 1.0f / (1.0f + expf(-z)) : silu_f32(z);
+    orow[i] = from_float<TO>(o[i] * inv * w[i] * gate_v);
+  }
 }
 
 template <int DREG, int MAXT>
@@ -424,9 +430,308 @@ extern "C" int cretif_delta_recurrence(const float* prep, int ldp, const float* 
   const unsigned blocks = (unsigned)((items + 7) / 8);
   if (out_dt == kF32)
     delta_out_norm_kernel<float><<<blocks, 256, 0, st>>>(o_raw, gate, ldg, norm_w, eps,
-                                                         (float*)out, ldo, H, e, items);
+                                                         (float*)out, ldo, H, e, items, 0, 0);
   else
     delta_out_norm_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
-        o_raw, gate, ldg, norm_w, eps, (__nv_bfloat16*)out, ldo, H, e, items);
+        o_raw, gate, ldg, norm_w, eps, (__nv_bfloat16*)out, ldo, H, e, items, 0, 0);
+  return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------
+// The generalized delta rule: decay and removal rate per key channel, removal along the key
+// at unit length.  Per token and head, with state M [d, e] (32-bit, zero at a sequence's start):
+//     x = M^T u;   M <- diag(w) M - b x^T + k v^T;   o = M^T r          (u, b, w, k, r in R^d)
+// where both products read the old M.  With u the key scaled to unit length, b = a * u for a
+// removal rate a in (0, 1) per channel and w in (0, 1) per channel this is the rule in which a
+// token first forgets (w), then takes out what the state holds along its key (a), then writes.
+// (The gated rule above is the case w = g, u = k, b = beta g k, v scaled by beta.)
+//
+// * general_delta_prepare (a warp per head of a token): u = k / sqrt(|k|^2 + unit_eps),
+//   b = sigmoid(a_proj + a_bias) * u, w = exp(-decay_scale * sigmoid(W2 tanh(w1) + w0)), where
+//   w1 is the token's low-rank projection (rank R, any size) and W2 [H d, R] expands it; the
+//   tanh of the R numbers is computed once per CTA into shared memory.
+// * general_delta_recurrence: the thread layout of delta_recurrence above -- a CTA per
+//   (sequence, head, slice of columns), P lanes a column, each lane a slice of the column's d
+//   rows in registers, a chunk's operands staged in shared memory by asynchronous copies a
+//   chunk ahead -- with five vectors a token (r, k, u, b, w) instead of two.  r, k and v are
+//   read from the projection's rows as they are.
+// * delta_out_norm (above) norms the read-outs per head, here with a weight per head and the
+//   logistic function of the gate.
+namespace cretif {
+
+constexpr int kGenChunk = 8;
+
+// proj row: [r (H d) | k (H d) | v (H e) | gate (H e) | a (H d) | w1 (R)]
+// prep row: [u (H d) | b (H d) | w (H d)]
+__global__ void __launch_bounds__(kPrepWarps * 32)
+general_delta_prepare_kernel(const float* __restrict__ proj, int ldp, float* __restrict__ prep,
+                             int ldo, const float* __restrict__ a_bias,
+                             const float* __restrict__ w2, const float* __restrict__ w0, int R,
+                             int H, int d, int e, float unit_eps, float decay_scale) {
+  extern __shared__ float th[];                   // tanh of the token's low-rank projection
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const float* row = proj + (size_t)t * ldp;
+  const int w1_at = 3 * H * d + 2 * H * e;
+  for (int j = threadIdx.x; j < R; j += blockDim.x) th[j] = tanhf(row[w1_at + j]);
+  __syncthreads();
+  const int h = blockIdx.y * kPrepWarps + warp;
+  if (h >= H) return;
+  float* out = prep + (size_t)t * ldo;
+  const float* k = row + (size_t)H * d + (size_t)h * d;
+  const float* a = row + (size_t)2 * H * d + (size_t)2 * H * e + (size_t)h * d;
+  float kv[kPrepMaxD / 32];
+  float ss = 0.f;
+#pragma unroll
+  for (int m = 0; m < kPrepMaxD / 32; ++m) {
+    const int i = lane + 32 * m;
+    kv[m] = i < d ? k[i] : 0.f;
+    ss += kv[m] * kv[m];
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss + unit_eps);
+#pragma unroll
+  for (int m = 0; m < kPrepMaxD / 32; ++m) {
+    const int i = lane + 32 * m;
+    if (i >= d) continue;
+    const int c = h * d + i;
+    const float u = kv[m] * inv;
+    const float rate = 1.0f / (1.0f + expf(-(a[i] + a_bias[c])));
+    float z = 0.f;
+    const float* w2row = w2 + (size_t)c * R;
+    for (int j = 0; j < R; ++j) z = fmaf(w2row[j], th[j], z);
+    z += w0[c];
+    const float decay = expf(-decay_scale / (1.0f + expf(-z)));
+    out[c] = u;
+    out[(size_t)H * d + c] = rate * u;
+    out[(size_t)2 * H * d + c] = decay;
+  }
+}
+
+template <int DREG, int MAXT>
+__global__ void __launch_bounds__(MAXT)
+general_delta_recurrence_kernel(const float* __restrict__ proj, int ldp,
+                                const float* __restrict__ prep, int ldq,
+                                float* __restrict__ state, size_t state_stride,
+                                const int* __restrict__ cu_seqlens,
+                                const int* __restrict__ seq_slot, int H, int d, int e, int P,
+                                int ecols, float* __restrict__ o_raw, int write_state, int vec) {
+  extern __shared__ __align__(16) float sm[];
+  const int b = blockIdx.x, h = blockIdx.y;
+  constexpr int kSlice = DREG + 4;               // see delta_recurrence_kernel
+  const int dpad = P * kSlice;
+  // a stage: r, k, u, b, w [kGenChunk][dpad] each, v [kGenChunk][ecols]
+  const int stage_floats = kGenChunk * (5 * dpad + ecols);
+  const int col0 = blockIdx.z * ecols;
+  const int tid = threadIdx.x, part = tid % P, jl = tid / P, j = col0 + jl;
+  const bool active = jl < ecols;
+  float* M = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e;
+  float S[DREG];
+#pragma unroll
+  for (int r = 0; r < DREG; ++r) {
+    const int i = part * DREG + r;
+    S[r] = (active && i < d) ? M[(size_t)i * e + j] : 0.f;
+  }
+  const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
+  for (int idx = tid; idx < 2 * stage_floats; idx += blockDim.x) sm[idx] = 0.f;
+  __syncthreads();
+  const size_t Hd = (size_t)H * d;
+  auto issue = [&](int s, int c0) {
+    float* base = sm + s * stage_floats;
+    float* vs = base + 5 * kGenChunk * dpad;
+    const int n = min(kGenChunk, t1 - c0);
+    // vector x of token tt, rows i..: from the projection (r, k) or the prepared row (u, b, w)
+    auto src = [&](int x, int tt, int i) -> const float* {
+      return x < 2 ? proj + (size_t)(c0 + tt) * ldp + (size_t)x * Hd + (size_t)h * d + i
+                   : prep + (size_t)(c0 + tt) * ldq + (size_t)(x - 2) * Hd + (size_t)h * d + i;
+    };
+    if (vec) {
+      const int d4 = d >> 2, e4 = ecols >> 2;
+      for (int idx = tid; idx < 5 * n * d4; idx += blockDim.x) {
+        const int x = idx / (n * d4), rem = idx - x * (n * d4);
+        const int tt = rem / d4, i = (rem - tt * d4) << 2;
+        cp_async16(base + (x * kGenChunk + tt) * dpad + (i / DREG) * kSlice + (i % DREG),
+                   src(x, tt, i));
+      }
+      for (int idx = tid; idx < n * e4; idx += blockDim.x) {
+        const int tt = idx / e4, i = (idx - tt * e4) << 2;
+        cp_async16(vs + tt * ecols + i,
+                   proj + (size_t)(c0 + tt) * ldp + 2 * Hd + (size_t)h * e + col0 + i);
+      }
+    } else {
+      for (int idx = tid; idx < 5 * n * d; idx += blockDim.x) {
+        const int x = idx / (n * d), rem = idx - x * (n * d);
+        const int tt = rem / d, i = rem - tt * d;
+        cp_async4(base + (x * kGenChunk + tt) * dpad + (i / DREG) * kSlice + (i % DREG),
+                  src(x, tt, i));
+      }
+      for (int idx = tid; idx < n * ecols; idx += blockDim.x) {
+        const int tt = idx / ecols, i = idx - tt * ecols;
+        cp_async4(vs + idx, proj + (size_t)(c0 + tt) * ldp + 2 * Hd + (size_t)h * e + col0 + i);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (t0 < t1) issue(0, t0);
+  int s = 0;
+  for (int c0 = t0; c0 < t1; c0 += kGenChunk, s ^= 1) {
+    const int n = min(kGenChunk, t1 - c0);
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();          // stage s has arrived; the other stage is read no more
+    if (c0 + kGenChunk < t1) issue(s ^ 1, c0 + kGenChunk);
+    const float* base = sm + s * stage_floats;
+    const float* vs = base + 5 * kGenChunk * dpad;
+    float* orow = o_raw + (size_t)c0 * H * e + (size_t)h * e + j;
+    for (int tt = 0; tt < n; ++tt) {
+      const int off = tt * dpad + part * kSlice;
+      const float4* r4 = reinterpret_cast<const float4*>(base + off);
+      const float4* k4 = reinterpret_cast<const float4*>(base + kGenChunk * dpad + off);
+      const float4* u4 = reinterpret_cast<const float4*>(base + 2 * kGenChunk * dpad + off);
+      const float4* b4 = reinterpret_cast<const float4*>(base + 3 * kGenChunk * dpad + off);
+      const float4* w4 = reinterpret_cast<const float4*>(base + 4 * kGenChunk * dpad + off);
+      const float vj = active ? vs[tt * ecols + jl] : 0.f;
+      // what the old state holds along the unit key, in four chains
+      float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
+#pragma unroll
+      for (int q = 0; q < DREG / 4; ++q) {
+        const float4 u = u4[q];
+        x0 = fmaf(S[4 * q], u.x, x0);
+        x1 = fmaf(S[4 * q + 1], u.y, x1);
+        x2 = fmaf(S[4 * q + 2], u.z, x2);
+        x3 = fmaf(S[4 * q + 3], u.w, x3);
+      }
+      float x = (x0 + x1) + (x2 + x3);
+      for (int o = P >> 1; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+      // decay, removal and write on every row the lane holds, then the read-out's chains
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int q = 0; q < DREG / 4; ++q) {
+        const float4 w = w4[q], bb = b4[q], kk = k4[q], rr = r4[q];
+        S[4 * q] = fmaf(kk.x, vj, fmaf(-bb.x, x, w.x * S[4 * q]));
+        S[4 * q + 1] = fmaf(kk.y, vj, fmaf(-bb.y, x, w.y * S[4 * q + 1]));
+        S[4 * q + 2] = fmaf(kk.z, vj, fmaf(-bb.z, x, w.z * S[4 * q + 2]));
+        S[4 * q + 3] = fmaf(kk.w, vj, fmaf(-bb.w, x, w.w * S[4 * q + 3]));
+        a0 = fmaf(S[4 * q], rr.x, a0);
+        a1 = fmaf(S[4 * q + 1], rr.y, a1);
+        a2 = fmaf(S[4 * q + 2], rr.z, a2);
+        a3 = fmaf(S[4 * q + 3], rr.w, a3);
+      }
+      float acc = (a0 + a1) + (a2 + a3);
+      for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (active && part == 0) orow[(size_t)tt * H * e] = acc;
+    }
+  }
+  if (write_state) {
+#pragma unroll
+    for (int r = 0; r < DREG; ++r) {
+      const int i = part * DREG + r;
+      if (active && i < d) M[(size_t)i * e + j] = S[r];
+    }
+  }
+}
+
+template <int DREG, int MAXT>
+static int launch_general_t(const float* proj, int ldp, const float* prep, int ldq, float* state,
+                            size_t state_stride, const int* cu, const int* seq_slot, int B, int H,
+                            int d, int e, int P, int ecols, float* o_raw, int write_state,
+                            int threads, cudaStream_t st) {
+  const size_t stage = (size_t)kGenChunk * (5 * P * (DREG + 4) + ecols);
+  const size_t smem = sizeof(float) * 2 * stage;
+  auto kern = general_delta_recurrence_kernel<DREG, MAXT>;
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) return kBadArgument;
+    cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem);
+    if (err != cudaSuccess) return (int)err;
+  }
+  const int vec = ldp % 4 == 0 && ldq % 4 == 0 && d % 4 == 0 && e % 4 == 0 && ecols % 4 == 0 &&
+                  (((uintptr_t)proj | (uintptr_t)prep) & 15) == 0;
+  kern<<<dim3(B, H, e / ecols), threads, smem, st>>>(proj, ldp, prep, ldq, state, state_stride, cu,
+                                                     seq_slot, H, d, e, P, ecols, o_raw,
+                                                     write_state, vec);
+  return launch_status();
+}
+
+template <int DREG>
+static int launch_general(const float* proj, int ldp, const float* prep, int ldq, float* state,
+                          size_t state_stride, const int* cu, const int* seq_slot, int B, int H,
+                          int d, int e, int P, int ecols, float* o_raw, int write_state,
+                          cudaStream_t st) {
+  const int threads = ((ecols * P + 31) / 32) * 32;
+  if (threads <= 512)
+    return launch_general_t<DREG, 512>(proj, ldp, prep, ldq, state, state_stride, cu, seq_slot, B,
+                                       H, d, e, P, ecols, o_raw, write_state, threads, st);
+  return launch_general_t<DREG, 1024>(proj, ldp, prep, ldq, state, state_stride, cu, seq_slot, B,
+                                      H, d, e, P, ecols, o_raw, write_state, threads, st);
+}
+
+}  // namespace cretif
+
+extern "C" int cretif_general_delta_prepare(const float* proj, int ldp, float* prep, int ldo,
+                                            const float* a_bias, const float* w2, const float* w0,
+                                            int R, int H, int d, int e, float unit_eps,
+                                            float decay_scale, int T, void* stream) {
+  if (T <= 0) return kOk;
+  if (H <= 0 || d <= 0 || e <= 0 || R <= 0 || R > 8192 || d > kPrepMaxD) return kBadArgument;
+  if (ldp < 3 * H * d + 2 * H * e + R || ldo < 3 * H * d) return kBadArgument;
+  dim3 grid(T, (H + kPrepWarps - 1) / kPrepWarps);
+  if (grid.y > 65535) return kBadArgument;
+  general_delta_prepare_kernel<<<grid, kPrepWarps * 32, sizeof(float) * R, (cudaStream_t)stream>>>(
+      proj, ldp, prep, ldo, a_bias, w2, w0, R, H, d, e, unit_eps, decay_scale);
+  return launch_status();
+}
+
+// per_head_weight: norm_w holds H * e numbers (else e, shared by the heads); gate_sigmoid: the
+// gate is the logistic function of its projection (else SiLU).
+extern "C" int cretif_general_delta_recurrence(
+    const float* proj, int ldp, const float* prep, int ldq, const float* gate, int ldg,
+    float* state, long long state_stride, const int* cu_seqlens, const int* seq_slot, int B, int H,
+    int d, int e, const float* norm_w, int per_head_weight, int gate_sigmoid, float eps,
+    float* o_raw, void* out, int out_dt, int ldo, int write_state, int T, void* stream) {
+  if (B <= 0 || T <= 0) return kOk;
+  if (H <= 0 || d <= 0 || e <= 0 || !o_raw) return kBadArgument;
+  if (out_dt != kF32 && out_dt != kBF16) return kBadDType;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  // the same plan as cretif_delta_recurrence: up to 32 rows a lane, a head's columns in slices
+  // while the (sequence, head) pairs alone do not fill the chip twice over
+  int P = 1;
+  while (P < 32 && (d + P - 1) / P > 32) P *= 2;
+  int ecols = e;
+  while ((long long)B * H * (e / ecols) < 2LL * sm_count && ecols % 2 == 0 && ecols / 2 >= 32)
+    ecols /= 2;
+  while (ecols * P > 1024 && ecols % 2 == 0 && ecols > 1) ecols /= 2;
+  while (ecols * P > 1024 && P > 1) P /= 2;
+  if (ecols * P > 1024) return kBadArgument;
+  const int rows = (d + P - 1) / P;
+  if (rows > 128) return kBadArgument;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc;
+#define CRETIF_GDELTA(DREG)                                                                     \
+  launch_general<DREG>(proj, ldp, prep, ldq, state, (size_t)state_stride, cu_seqlens, seq_slot, \
+                       B, H, d, e, P, ecols, o_raw, write_state, st)
+  if (rows <= 8) rc = CRETIF_GDELTA(8);
+  else if (rows <= 16) rc = CRETIF_GDELTA(16);
+  else if (rows <= 32) rc = CRETIF_GDELTA(32);
+  else if (rows <= 64) rc = CRETIF_GDELTA(64);
+  else rc = CRETIF_GDELTA(128);
+#undef CRETIF_GDELTA
+  if (rc) return rc;
+  const long long items = (long long)T * H;
+  const unsigned blocks = (unsigned)((items + 7) / 8);
+  const int w_stride = per_head_weight ? e : 0;
+  if (out_dt == kF32)
+    delta_out_norm_kernel<float><<<blocks, 256, 0, st>>>(o_raw, gate, ldg, norm_w, eps,
+                                                         (float*)out, ldo, H, e, items, w_stride,
+                                                         gate_sigmoid);
+  else
+    delta_out_norm_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+        o_raw, gate, ldg, norm_w, eps, (__nv_bfloat16*)out, ldo, H, e, items, w_stride,
+        gate_sigmoid);
   return launch_status();
 }

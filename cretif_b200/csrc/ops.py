@@ -345,29 +345,260 @@ def delta_recurrence(prep, gate, state, cu_seqlens, seq_slot, B: int, H: int, G:
         int(write_state), T, _stream()), "delta_recurrence", kernels=2)
 
 
+# ------------------------------------------------------------------ Dynamic Tanh, token shift
+def dyt_rows(h, delta, weight, bias, alpha, out, gain=None, rows=None, write_h: bool = True) -> None:
+    """out[r] = (tanh(alpha v) w + b) gain with v = h[src] (+ delta[src]); ``alpha`` is a
+    one-element float32 tensor on the device."""
+    _need(h, "h", torch.float32, 2); _need(out, "out", dim=2)
+    H = h.shape[1]
+    for name, t in (("weight", weight), ("bias", bias), ("gain", gain)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.numel() != H or not t.is_contiguous():
+                raise KernelError(f"dyt_rows: {name} must have {H} elements")
+    _need(alpha, "alpha", torch.float32)
+    if not h.is_contiguous() or not out.is_contiguous() or alpha.numel() != 1:
+        raise KernelError("dyt_rows: h and out must be contiguous and alpha one number")
+    if delta is not None:
+        _need(delta, "delta", dim=2)
+        if delta.shape != h.shape or not delta.is_contiguous():
+            raise KernelError("dyt_rows: delta must match h")
+    R = h.shape[0] if rows is None else rows.numel()
+    if tuple(out.shape) != (R, H):
+        raise KernelError(f"dyt_rows: out must be [{R}, {H}]")
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    _check(lib().cretif_dyt_rows(
+        _p(h), _p(delta), 0 if delta is None else _dt(delta), _p(weight), _p(bias), _p(alpha),
+        _p(gain), _p(out), _dt(out), _p(rows), R, H,
+        int(write_h and rows is None and delta is not None), _stream()), "dyt_rows")
+
+
+def dyt_add(h, y, weight, bias, alpha, gain=None) -> None:
+    """h += (tanh(alpha y) w + b) gain, element by element, in 32-bit."""
+    _need(h, "h", torch.float32, 2); _need(y, "y", dim=2)
+    R, H = h.shape
+    if tuple(y.shape) != (R, H) or not h.is_contiguous() or weight.numel() != H \
+            or bias.numel() != H or (gain is not None and gain.numel() != H) or alpha.numel() != 1:
+        raise KernelError("dyt_add: y must match h and the weights have H elements")
+    for t in (weight, bias, alpha) + ((gain,) if gain is not None else ()):
+        _need(t, "weight", torch.float32)
+    _check(lib().cretif_dyt_add(_p(h), _p(y), _dt(y), _rows(y, "y"), _p(weight), _p(bias),
+                                _p(alpha), _p(gain), R, H, _stream()), "dyt_add")
+
+
+def shift_rows(h, shift, state, tok_seq, seq_slot, cu_seqlens, out, weight=None, bias=None,
+               alpha=None) -> None:
+    """out[t] = n[t] + (n[t-1] - n[t]) * shift, n = dyt(h) when weight/bias/alpha are given, else
+    n = h.  A sequence's first token of the step reads ``state[slot]`` (float32 [slots, H]) and
+    leaves the step's last row there."""
+    _need(h, "h", torch.float32, 2); _need(shift, "shift", torch.float32, 1)
+    _need(state, "state", torch.float32, 2); _need(out, "out", dim=2)
+    T, H = h.shape
+    if (not h.is_contiguous() or not out.is_contiguous() or tuple(out.shape) != (T, H)
+            or shift.numel() != H or state.shape[1] != H or state.stride(1) != 1):
+        raise KernelError("shift_rows: sizes do not fit")
+    if weight is not None:
+        for t in (weight, bias, alpha):
+            _need(t, "norm weight", torch.float32)
+        if weight.numel() != H or bias.numel() != H or alpha.numel() != 1:
+            raise KernelError("shift_rows: the norm's weights have H elements")
+    _check(lib().cretif_shift_rows(
+        _p(h), _p(weight), _p(bias), _p(alpha), _p(shift), _p(state),
+        ctypes.c_longlong(state.stride(0)), _p(tok_seq), _p(seq_slot), _p(cu_seqlens), _p(out),
+        _dt(out), T, H, _stream()), "shift_rows")
+
+
+# ------------------------------------------------------------------ convolved attention inputs
+def conv_headnorm_kv_append(proj, conv_w, conv_state, tok_pos, tok_seq, seq_slot, seq_start,
+                            nh: int, nkv: int, hd: int, vd: int, eps: float, gain_coef: float,
+                            gain_every: int, q_out, table=None, kc=None, vc=None,
+                            block_tokens: int = 0, write_cache: bool = True, fault=None) -> None:
+    """``proj`` float32 [T, nh·hd + nkv·(hd + vd)] -> convolution over time, unit RMS per q/k
+    head, the query's gain by position; q into ``q_out``, k and v into the block cache.  ``nkv``
+    0: queries only.  ``conv_state`` [slots, C·(taps-1)] holds every slot's last inputs."""
+    _need(proj, "proj", torch.float32, 2); _need(conv_w, "conv_w", torch.float32, 2)
+    _need(q_out, "q_out", dim=2)
+    C, taps = conv_w.shape
+    if C != nh * hd + nkv * (hd + vd) or not conv_w.is_contiguous() or proj.shape[1] < C:
+        raise KernelError("conv_headnorm_kv_append: the convolution's sizes do not fit")
+    if taps > 1:
+        _need(conv_state, "conv_state", torch.float32, 2)
+        if conv_state.stride(1) != 1 or conv_state.shape[1] != C * (taps - 1):
+            raise KernelError("conv_headnorm_kv_append: conv_state must be [slots, C (taps-1)]")
+    if q_out.shape[0] != proj.shape[0] or q_out.shape[1] < nh * hd:
+        raise KernelError("conv_headnorm_kv_append: q_out must be [tokens, heads*head_dim]")
+    if nkv > 0:
+        _need(kc, "k cache", q_out.dtype, 4); _need(vc, "v cache", q_out.dtype, 4)
+        if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
+                or tuple(vc.shape[1:]) != (nkv, block_tokens, vd) or not vc.is_contiguous()):
+            raise KernelError("conv_headnorm_kv_append: caches must be contiguous "
+                              "[blocks, kv_heads, block, head_dim / value_dim]")
+    _check(lib().cretif_conv_headnorm_kv_append(
+        _p(proj), _rows(proj, "proj"), _p(conv_w), taps, _p(conv_state if taps > 1 else None),
+        ctypes.c_longlong(conv_state.stride(0) if taps > 1 else 0), _p(tok_pos), _p(tok_seq),
+        _p(seq_slot), _p(seq_start), nh, nkv, hd, vd, ctypes.c_float(eps),
+        ctypes.c_float(gain_coef), int(gain_every), _p(q_out), _rows(q_out, "q_out"), _dt(q_out),
+        _p(table), 0 if table is None else table.stride(0), _p(kc), _p(vc), block_tokens,
+        int(write_cache), proj.shape[0], _p(fault), _stream()), "conv_headnorm_kv_append")
+
+
+# ------------------------------------------------------------------ generalized delta rule
+def general_delta_prepare(proj, prep, a_bias, w2, w0, H: int, d: int, e: int, unit_eps: float,
+                          decay_scale: float) -> None:
+    """``proj`` float32 [T, 3Hd + 2He + R] = [r | k | v | gate | a | w1]; ``prep`` [T, 3Hd] =
+    [unit key | removal along it | decay], see delta_rule.cu."""
+    _need(proj, "proj", torch.float32, 2); _need(prep, "prep", torch.float32, 2)
+    _need(w2, "w2", torch.float32, 2); _need(w0, "w0", torch.float32, 1)
+    _need(a_bias, "a_bias", torch.float32, 1)
+    R = w2.shape[1]
+    if (w2.shape[0] != H * d or not w2.is_contiguous() or w0.numel() != H * d
+            or a_bias.numel() != H * d or proj.shape[1] < 3 * H * d + 2 * H * e + R
+            or prep.shape[1] < 3 * H * d or prep.shape[0] != proj.shape[0]):
+        raise KernelError("general_delta_prepare: sizes do not fit")
+    _check(lib().cretif_general_delta_prepare(
+        _p(proj), _rows(proj, "proj"), _p(prep), _rows(prep, "prep"), _p(a_bias), _p(w2), _p(w0),
+        R, H, d, e, ctypes.c_float(unit_eps), ctypes.c_float(decay_scale), proj.shape[0],
+        _stream()), "general_delta_prepare")
+
+
+def general_delta_recurrence(proj, prep, gate, state, cu_seqlens, seq_slot, B: int, H: int, d: int,
+                             e: int, norm_w, eps: float, out, per_head_weight: bool = True,
+                             gate_sigmoid: bool = True, write_state: bool = True) -> None:
+    """The generalized delta rule over the step's tokens of every (sequence, head), from and to
+    ``state`` (view [slots, H·d·e] float32), then the per-head RMS norm times ``norm_w`` times
+    the gate -> ``out`` [T, H·e]."""
+    _need(proj, "proj", torch.float32, 2); _need(prep, "prep", torch.float32, 2)
+    _need(gate, "gate", torch.float32, 2); _need(state, "state", torch.float32, 2)
+    _need(out, "out", dim=2); _need(norm_w, "norm_w", torch.float32, 1)
+    T = proj.shape[0]
+    if (state.stride(1) != 1 or state.shape[1] < H * d * e or out.shape[0] != T
+            or out.shape[1] < H * e or norm_w.numel() != (H * e if per_head_weight else e)):
+        raise KernelError("general_delta_recurrence: sizes do not fit")
+    o_raw = torch.empty((T, H * e), dtype=torch.float32, device=proj.device)
+    _check(lib().cretif_general_delta_recurrence(
+        _p(proj), _rows(proj, "proj"), _p(prep), _rows(prep, "prep"), _p(gate),
+        _rows(gate, "gate"), _p(state), ctypes.c_longlong(state.stride(0)), _p(cu_seqlens),
+        _p(seq_slot), B, H, d, e, _p(norm_w), int(per_head_weight), int(gate_sigmoid),
+        ctypes.c_float(eps), _p(o_raw), _p(out), _dt(out), _rows(out, "out"), int(write_state), T,
+        _stream()), "general_delta_recurrence", kernels=2)
+
+
+# ------------------------------------------------------------------ routed experts
+MOE_TILE = 64
+_moe_simt_only = False
+
+
+def moe_simt_only(on: bool) -> None:
+    """Run the experts' products on the CUDA cores whatever the element type (the yardstick)."""
+    global _moe_simt_only
+    _moe_simt_only = bool(on)
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    return -(-pairs // MOE_TILE) + experts
+
+
+def moe_route(x, router_w, top: int, ids, wts, renorm: bool = False) -> None:
+    """ids/wts [T, top]: the ``top`` experts with the largest sigmoid(router_w · x) per token."""
+    _need(x, "x", dim=2); _need(router_w, "router_w", torch.float32, 2)
+    _need(ids, "ids", torch.int32, 2); _need(wts, "wts", torch.float32, 2)
+    T, H = x.shape
+    E = router_w.shape[0]
+    if (router_w.shape[1] != H or not router_w.is_contiguous() or tuple(ids.shape) != (T, top)
+            or tuple(wts.shape) != (T, top) or not ids.is_contiguous() or not wts.is_contiguous()):
+        raise KernelError("moe_route: sizes do not fit")
+    if not 0 < top <= E or E > 256:
+        raise KernelError(f"moe_route: {top} of {E} experts (at most 256) cannot be chosen")
+    _check(lib().cretif_moe_route(_p(x), _dt(x), _rows(x, "x"), _p(router_w), E, H, top,
+                                  int(renorm), _p(ids), _p(wts), T, _stream()), "moe_route")
+
+
+def moe_group(ids, experts: int, offsets, place, order, tile_expert, tile_row0) -> None:
+    """Sort the (token, choice) pairs by expert: ``offsets`` [E + 1], ``place`` [P] (a pair's
+    row in the sorted list), ``order`` [P] (its inverse) and the list of 64-row tiles."""
+    for name, t in (("ids", ids), ("offsets", offsets), ("place", place), ("order", order),
+                    ("tile_expert", tile_expert), ("tile_row0", tile_row0)):
+        _need(t, name, torch.int32)
+        if not t.is_contiguous():
+            raise KernelError(f"moe_group: {name} must be contiguous")
+    P = ids.numel()
+    if (offsets.numel() != experts + 1 or place.numel() != P or order.numel() != P
+            or tile_expert.numel() != tile_row0.numel()
+            or tile_expert.numel() < moe_max_tiles(P, experts)):
+        raise KernelError("moe_group: sizes do not fit")
+    _check(lib().cretif_moe_group(_p(ids), P, experts, _p(offsets), _p(place), _p(order),
+                                  _p(tile_expert), _p(tile_row0), tile_expert.numel(), _stream()),
+           "moe_group")
+
+
+def moe_gemm(a, w, c, top: int, mode: int, scale_at: int, wts, order, offsets, tile_expert,
+             tile_row0) -> None:
+    """Grouped product over the sorted rows.  mode 0: ``a`` [tokens, K], ``w`` [E, 2N, K]
+    (gate rows then up rows), ``c`` [P, N] = silu(s g)(s u) (scale_at 1) or silu(g) u; mode 1:
+    ``a`` [P, K] sorted rows, ``w`` [E, N, K], ``c`` [P, N] float32 (scale_at 2: times s)."""
+    _need(a, "a", dim=2); _need(w, "w", a.dtype, 3); _need(c, "c", dim=2)
+    K = a.shape[1]
+    N = c.shape[1]
+    if (w.shape[2] != K or w.shape[1] != (2 * N if mode == 0 else N) or not w.is_contiguous()
+            or c.dtype != (a.dtype if mode == 0 else torch.float32) or c.shape[0] != order.numel()):
+        raise KernelError("moe_gemm: sizes or element types do not fit")
+    use_mma = int(a.dtype == torch.bfloat16 and not _moe_simt_only)
+    _check(lib().cretif_moe_gemm(
+        _p(a), _dt(a), _rows(a, "a"), _p(w), _dt(w), _p(c), _rows(c, "c"), N, K, top, mode,
+        scale_at, _p(wts), _p(order), _p(offsets), _p(tile_expert), _p(tile_row0),
+        tile_expert.numel(), use_mma, _stream()), "moe_gemm")
+
+
+def moe_combine(rows, place, top: int, y) -> None:
+    """y[t] = the sum of the token's ``top`` rows of ``rows`` (float32), in their order."""
+    _need(rows, "rows", torch.float32, 2); _need(y, "y", torch.float32, 2)
+    _need(place, "place", torch.int32)
+    T, H = y.shape
+    if rows.shape[1] != H or place.numel() != T * top or not y.is_contiguous():
+        raise KernelError("moe_combine: sizes do not fit")
+    _check(lib().cretif_moe_combine(_p(rows), _rows(rows, "rows"), _p(place), top, _p(y), T, H,
+                                    _stream()), "moe_combine")
+
+
 # ------------------------------------------------------------------ attention
 def attn_simt(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
-              scale: float, window: int, block_tokens: int, sink=None) -> None:
+              scale: float, window: int, block_tokens: int, sink=None, vd: int = 0, bias=None,
+              bias_edges=None) -> None:
     """``sink`` (float32 [heads], optional): exp(sink_h) joins head h's softmax denominator
-    without a key or a value."""
+    without a key or a value.  ``vd``: size of a value head when it is not ``hd``.  ``bias``
+    (float32 [rows, heads]) with ``bias_edges`` (int32 [rows], ascending from 0): the key n
+    positions back adds ``bias[r, h]`` to its scaled score, r the last row with edge <= n."""
     _need(q, "q", dim=2); _need(out, "out", q.dtype, 2)
     _need(kc, "k cache", q.dtype, 4); _need(vc, "v cache", q.dtype, 4)
     T = q.shape[0]
-    if out.shape[0] != T or out.shape[1] < nh * hd or q.shape[1] < nh * hd:
-        raise KernelError("attention: q/out must hold [tokens, heads*head_dim]")
+    vd = vd or hd
+    if out.shape[0] != T or out.shape[1] < nh * vd or q.shape[1] < nh * hd:
+        raise KernelError("attention: q must hold [tokens, heads*head_dim], out "
+                          "[tokens, heads*value_dim]")
     if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
-            or not vc.is_contiguous()):
-        raise KernelError("attention: cache must be contiguous [blocks, kv_heads, block, head_dim]")
-    if hd <= 0 or hd > 512:
-        raise KernelError(f"attention: head_dim {hd} is not in [1, 512]")
+            or tuple(vc.shape[1:]) != (nkv, block_tokens, vd) or not vc.is_contiguous()):
+        raise KernelError("attention: caches must be contiguous [blocks, kv_heads, block, "
+                          "head_dim] and [..., value_dim]")
+    if hd <= 0 or hd > 512 or vd > 512:
+        raise KernelError(f"attention: head sizes {hd}, {vd} are not in [1, 512]")
     if sink is not None:
         _need(sink, "sink", torch.float32, 1)
         if sink.numel() != nh or not sink.is_contiguous():
             raise KernelError("attention: the sink has one number per query head")
+    rows = 0
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 2); _need(bias_edges, "bias_edges", torch.int32, 1)
+        rows = bias.shape[0]
+        if (bias.shape[1] != nh or not bias.is_contiguous() or bias_edges.numel() != rows
+                or not bias_edges.is_contiguous() or not 0 < rows <= 1024):
+            raise KernelError("attention: the distance bias is [rows <= 1024, heads] with one "
+                              "edge per row")
     _check(lib().cretif_attn_simt(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _dt(q), _p(kc), _p(vc), _p(table),
         table.stride(0), _p(tok_pos), _p(tok_seq), _p(seq_slot), nh, nkv, hd,
-        ctypes.c_float(scale), window, block_tokens, T, _p(sink), _stream()), "attn_simt")
+        ctypes.c_float(scale), window, block_tokens, T, _p(sink), vd, _p(bias), _p(bias_edges),
+        rows, _stream()), "attn_simt")
 
 
 # ------------------------------------------------------------------ sampling

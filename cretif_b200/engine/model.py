@@ -14,6 +14,7 @@ from typing import Any, Callable, Dict, List, Optional, Set, Tuple
 
 import torch
 
+from ..cache import KVRequest
 from ..config.spec import BranchSpec, ModelSpec, PartSpec
 from ..parts.base import LayerCache, Part, StepContext, build_part, lookup_part
 from ..weights.loader import WeightSpec
@@ -27,9 +28,10 @@ class Branch:
     part: Part
     norm: Optional[Part] = None
     post_norm: Optional[Part] = None
+    shift: Optional[Part] = None   # between the norm and the part
 
     def parts(self) -> List[Part]:
-        return [p for p in (self.norm, self.part, self.post_norm) if p is not None]
+        return [p for p in (self.norm, self.shift, self.part, self.post_norm) if p is not None]
 
 
 @dataclass
@@ -47,6 +49,8 @@ def _branch_specs(bs: BranchSpec):
     """(category, PartSpec) of a branch's parts, in the order they are built and loaded."""
     if bs.norm is not None:
         yield "norm", bs.norm
+    if bs.shift is not None:
+        yield "shift", bs.shift
     yield bs.role, bs.part
     if bs.post_norm is not None:
         yield "norm", bs.post_norm
@@ -97,9 +101,10 @@ class Model:
             branches = []
             for bs in ls.branches:
                 norm = next(it) if bs.norm is not None else None
+                shift = next(it) if bs.shift is not None else None
                 part = next(it)
                 post = next(it) if bs.post_norm is not None else None
-                branches.append(Branch(bs.role, part, norm, post))
+                branches.append(Branch(bs.role, part, norm, post, shift))
             self.layers.append(Layer(ls.prefix, branches,
                                      lookup_part("arrangement", ls.arrangement)))
         self.final_norm = next(it)
@@ -131,21 +136,30 @@ class Model:
                 part.prepare(max_positions)
 
     # -- cache -------------------------------------------------------------------
-    def cache_requests(self) -> Dict[Tuple[int, int], Any]:
-        """cache id → what its part keeps between steps.  A cache id is (index of the owning
-        schedule entry, index of the branch in its layer); only entries that own their cache
-        (``ScheduleEntry.cache is None``) appear."""
+    def cache_requests(self) -> Dict[Tuple, Any]:
+        """cache id → what its part keeps between steps.  A cache id is (index of the schedule
+        entry, index of the branch in its layer) for the branch's part and (entry, branch,
+        "shift") for a shift in front of it.  A part may ask for keys and values, for a state of
+        fixed size, or for both (a tuple).  An entry that borrows (``ScheduleEntry.cache``) reads
+        the owner's keys and values and asks for none; states are always an entry's own."""
         out = {}
         for i, entry in enumerate(self.spec.schedule):
-            if entry.cache is None:
-                for k, br in enumerate(self.layers[entry.layer].branches):
-                    if hasattr(br.part, "cache_request"):
-                        out[(i, k)] = br.part.cache_request()
+            for k, br in enumerate(self.layers[entry.layer].branches):
+                if hasattr(br.part, "cache_request"):
+                    reqs = br.part.cache_request()
+                    reqs = list(reqs) if isinstance(reqs, (tuple, list)) else [reqs]
+                    reqs = [r for r in reqs if r is not None
+                            and not (entry.cache is not None and isinstance(r, KVRequest))]
+                    if reqs:
+                        out[(i, k)] = reqs[0] if len(reqs) == 1 else tuple(reqs)
+                if br.shift is not None:
+                    out[(i, k, "shift")] = br.shift.cache_request()
         return out
 
     def layer_caches(self, i: int, cache) -> List[Optional[LayerCache]]:
-        """What each branch of schedule entry ``i`` is handed: its own cache, the cache of the
-        entry it borrows from (read-only), or None for a part that keeps nothing."""
+        """What each branch of schedule entry ``i`` is handed: its own keys/values or those of
+        the entry it borrows from (read-only), its own states, or None for a branch that keeps
+        nothing."""
         entry = self.spec.schedule[i]
         owner = i if entry.cache is None else entry.cache
         views: List[Optional[LayerCache]] = []
@@ -159,9 +173,11 @@ class Model:
                     self.layers[self.spec.schedule[owner].layer].branches) if b.role == "mixer"]
                 cid = (owner, theirs[mine.index(k)])
             kv = cache.kv_view(cid) if cache.has_kv(cid) else None
-            state = cache.state_view(cid) if cache.has_state(cid) else None
-            views.append(None if kv is None and state is None
-                         else LayerCache(kv=kv, state=state, writes=entry.cache is None))
+            state = cache.state_view((i, k)) if cache.has_state((i, k)) else None
+            shift = cache.state_view((i, k, "shift")) if cache.has_state((i, k, "shift")) else None
+            views.append(None if kv is None and state is None and shift is None
+                         else LayerCache(kv=kv, state=state, writes=entry.cache is None,
+                                         shift_state=shift))
         return views
 
     # -- one step ------------------------------------------------------------------

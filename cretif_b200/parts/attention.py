@@ -12,13 +12,25 @@ Two options change what is projected and normed: ``qk_norm`` applies an RMS norm
 weight per channel over the WHOLE query projection and over the whole key projection (all
 heads of a token as one vector) before the heads are split; ``values: "keys"`` drops the value
 projection, the values being the keys as projected, before that norm.  ``sink`` names a tensor
-with one number per query head whose exponential joins the softmax's denominator.
+with one number per query head whose exponential joins the softmax's denominator
+(``fixed_sink`` gives every head the same constant instead: 0 adds one to the denominator).
+
+A second family of options serves attention whose projections pass a short causal
+convolution over time: ``conv`` (taps and the tensors' names; the last taps - 1 projected
+rows of a sequence are kept per cache slot), ``head_norm`` (q and k of every head divided by
+their root mean square, no weight), ``query_gain`` (the query times
+``1 + coef * ln(floor((pos + 1) / every) + 1)``), ``distance_bias`` (a learned table
+``[rows, heads]`` added to the scaled scores by distance: a row per distance below rows/2,
+beyond that rows spaced by the logarithm up to ``far``), ``value_dim`` (values of another
+size than the keys) and ``own_kv: False`` (no key and value tensors: the layer reads the keys
+and values that another schedule entry stores, with queries, bias and everything else of its
+own).  One kernel does convolution, head norm, gain and the cache write.
 """
 from __future__ import annotations
 
 import torch
 
-from ..cache import KVRequest
+from ..cache import KVRequest, StateRequest
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import WeightSpec
@@ -49,11 +61,35 @@ def force_plain_attention(on: bool) -> None:
     _force_plain = bool(on)
 
 
-def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None):
+def distance_edges(rows: int, far: float):
+    """The smallest distance of every row of a distance-bias table: row n for n < rows/2, then
+    ``rows/2 + floor(ln(n / (rows/2)) / ln(far / (rows/2)) * (rows - rows/2))`` capped at the last
+    row.  Computed once on the host in 64-bit; the kernels only search the edges."""
+    import numpy as np
+    half = rows // 2
+    if rows < 2 or not far > half:
+        raise ValueError(f"distance bias: {rows} rows need far > {half}, got {far}")
+    n = np.arange(half, int(np.ceil(far)) + 2, dtype=np.float64)
+    bucket = np.minimum(rows - 1, half + np.floor(np.log(n / half) / np.log(far / half)
+                                                  * (rows - half))).astype(np.int64)
+    edges = np.arange(rows, dtype=np.int64)
+    for b in range(half, rows):
+        edges[b] = half + int(np.argmax(bucket >= b))      # reached at far at the latest
+    return edges.astype(np.int32)
+
+
+def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, vd=0, bias=None,
+                  bias_edges=None):
     """Causal (windowed) attention of the step's queries ``q`` [T, nh·hd] over the cache view
     ``kv`` into ``o``, with the kernel that fits the step: the decode kernels when every
     sequence brings one token, the prompt kernel otherwise, the plain kernel for float32 and
-    for whatever the fast ones do not take."""
+    for whatever the fast ones do not take (a bias by distance, values of another size)."""
+    vd = vd or hd
+    if bias is not None or vd != hd:
+        ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
+                      nh, nkv, hd, scale, window, kv.block_tokens, sink=sink, vd=vd, bias=bias,
+                      bias_edges=bias_edges)
+        return
     if not _force_plain and dtype == torch.bfloat16 and (sink is None or hd <= 128):
         if ctx.is_decode and ops.attn_decode_supported(hd, kv.block_tokens, min(nh // nkv, 8)) \
                 and (nh // nkv <= 8 or nkv == 1):
@@ -116,17 +152,57 @@ class Attention(Part):
             raise ValueError("attention: qk_norm over the whole projection is built without a "
                              "position encoding only")
         self.sink = None
+        # -- the convolved family
+        self.vd = int(params.get("value_dim") or self.hd)
+        self.o_dim, self.v_dim = self.nh * self.vd, self.nkv * self.vd
+        self.own_kv = bool(params.get("own_kv", True))
+        self.conv = params.get("conv")
+        self.head_norm = params.get("head_norm")
+        self.query_gain = params.get("query_gain")
+        self.distance_bias = params.get("distance_bias")
+        self.bias = self.bias_edges = None
+        extras = [k for k in ("head_norm", "query_gain", "distance_bias") if params.get(k)] \
+            + (["value_dim"] if self.vd != self.hd else []) + ([] if self.own_kv else ["own_kv"])
+        if self.conv is None and extras:
+            raise ValueError(f"attention: {extras} are built for convolved projections "
+                             "(give `conv`)")
+        if self.conv is not None:
+            if self.head_norm is None or self.qk_norm is not None or self.values_are_keys \
+                    or (params.get("position") or {}).get("kind", "none") != "none":
+                raise ValueError("attention: convolved projections are built with head_norm, "
+                                 "without qk_norm, position encoding or keys as values")
+            if int(self.conv["taps"]) < 1 or not 1 <= self.vd <= 512:
+                raise ValueError("attention: conv.taps must be >= 1 and value_dim in [1, 512]")
+            self.taps = int(self.conv["taps"])
+            self.conv_channels = self.q_dim + (self.kv_dim + self.v_dim if self.own_kv else 0)
+        if params.get("fixed_sink") is not None and params.get("sink"):
+            raise ValueError("attention: give `sink` (a tensor) or `fixed_sink`, not both")
 
     @classmethod
     def weight_specs(cls, params, hidden_size):
         q = params["num_heads"] * params["head_dim"]
         kv = params["num_kv_heads"] * params["head_dim"]
+        vdim = params["num_kv_heads"] * (params.get("value_dim") or params["head_dim"])
+        o_in = params["num_heads"] * (params.get("value_dim") or params["head_dim"])
         n = params["names"]
         out = {"q": (n["q"], WeightSpec((q, hidden_size))),
-               "k": (n["k"], WeightSpec((kv, hidden_size))),
-               "o": (n["o"], WeightSpec((hidden_size, q)))}
-        if params.get("values", "projected") != "keys":
-            out["v"] = (n["v"], WeightSpec((kv, hidden_size)))
+               "o": (n["o"], WeightSpec((hidden_size, o_in)))}
+        own = params.get("own_kv", True)
+        if own:
+            out["k"] = (n["k"], WeightSpec((kv, hidden_size)))
+        if own and params.get("values", "projected") != "keys":
+            out["v"] = (n["v"], WeightSpec((vdim, hidden_size)))
+        conv = params.get("conv")
+        if conv:
+            taps = dict(init=(0.0, 0.5))
+            out["q_conv"] = (conv["q"], WeightSpec((q, conv["taps"]), **taps))
+            if own:
+                out["k_conv"] = (conv["k"], WeightSpec((kv, conv["taps"]), **taps))
+                out["v_conv"] = (conv["v"], WeightSpec((vdim, conv["taps"]), **taps))
+        if params.get("distance_bias"):
+            db = params["distance_bias"]
+            out["rel"] = (db["name"], WeightSpec((int(db.get("rows", 32)), params["num_heads"]),
+                                                 init=(0.0, 1.0), free=(0,)))
         if params.get("qk_norm"):
             out["q_norm"] = (params["qk_norm"]["q"], WeightSpec((q,), init=(1.0, 0.1)))
             out["k_norm"] = (params["qk_norm"]["k"], WeightSpec((kv,), init=(1.0, 0.1)))
@@ -136,8 +212,20 @@ class Attention(Part):
 
     def load(self, tensors):
         # one product for q, k and v: rows [q | k | v] of the stacked matrix
-        stacked = [tensors["q"], tensors["k"]] + ([] if self.values_are_keys else [tensors["v"]])
+        stacked = [tensors["q"]] + ([tensors["k"]] if self.own_kv else []) \
+            + ([tensors["v"]] if self.own_kv and not self.values_are_keys else [])
         self.w_qkv = self._matrix(torch.cat(stacked, dim=0))
+        if self.conv is not None:
+            taps = [tensors["q_conv"]] + ([tensors["k_conv"], tensors["v_conv"]]
+                                          if self.own_kv else [])
+            self.conv_w = self._vector32(torch.cat(taps, dim=0))
+        if self.distance_bias is not None:
+            self.bias = self._vector32(tensors["rel"])
+            self.bias_edges = torch.from_numpy(distance_edges(
+                self.bias.shape[0], float(self.distance_bias["far"]))).to(self.device)
+        if self.params.get("fixed_sink") is not None:
+            self.sink = torch.full((self.nh,), float(self.params["fixed_sink"]),
+                                   dtype=torch.float32, device=self.device)
         self.w_o = self._matrix(tensors["o"])
         if self.qk_norm is not None:
             self.q_norm_w = self._vector32(tensors["q_norm"])
@@ -152,12 +240,48 @@ class Attention(Part):
             self.position.prepare(max_positions)
 
     def cache_request(self):
-        return KVRequest(self.nkv, self.hd, self.window)
+        kv = KVRequest(self.nkv, self.hd, self.window,
+                       value_dim=0 if self.vd == self.hd else self.vd) if self.own_kv else None
+        if self.conv is None or self.taps == 1:
+            return kv
+        # the last taps - 1 projected rows of every convolved channel
+        state = StateRequest((self.conv_channels * (self.taps - 1),), torch.float32)
+        return state if kv is None else (kv, state)
+
+    def _forward_convolved(self, x, ctx, cache, into=None):
+        """Projections in 32-bit, then one kernel for convolution, head norm, the query's gain
+        and the cache write, the saved inputs brought up to date, attention, output product."""
+        from .linear import linear_few
+        kv = cache.kv
+        if kv is None:
+            raise ValueError("attention: this layer reads another entry's keys and values, but "
+                             "the schedule gives it none")
+        proj = linear_few(x, self.w_qkv, out_dtype=torch.float32)
+        q = torch.empty((ctx.T, self.q_dim), dtype=self.dtype, device=x.device)
+        gain = self.query_gain or {"coef": 0.0, "every": 0}
+        state = cache.state if self.taps > 1 else None
+        ops.conv_headnorm_kv_append(
+            proj, self.conv_w, state, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, ctx.seq_start,
+            self.nh, self.nkv if self.own_kv else 0, self.hd, self.vd,
+            float(self.head_norm["eps"]), float(gain["coef"]), int(gain["every"]), q,
+            table=kv.table, kc=kv.k, vc=kv.v, block_tokens=kv.block_tokens,
+            write_cache=cache.writes and self.own_kv, fault=ctx.fault)
+        if self.taps > 1:
+            ops.delta_conv_state(proj, state, self.taps, self.conv_channels, ctx.cu_seqlens,
+                                 ctx.seq_slot, ctx.B)
+        o = torch.empty((ctx.T, self.o_dim), dtype=self.dtype, device=x.device)
+        self.attend(q, o, ctx, kv)
+        if into is not None:
+            linear(o, self.w_o, out=into, accumulate=True)
+            return None
+        return linear_few(o, self.w_o, out_dtype=torch.float32)
 
     def forward(self, x, ctx, cache, into=None):
         """``into``: a float32 matrix that the output is added to (the residual stream) instead
         of being returned."""
         from .linear import plain_forced, skinny_max_rows
+        if self.conv is not None:
+            return self._forward_convolved(x, ctx, cache, into)
         kv = cache.kv
         rot = getattr(self.position, "rotary_table", None)
         rot = rot() if rot is not None else None         # (cos, sin, pairing, rotary_dim)
@@ -210,7 +334,7 @@ class Attention(Part):
         """bfloat16.  Few tokens: norm + q|k|v + rotary + cache write in one kernel, attention,
         then the output projection added into ``h``.  Many tokens: the same through the norm's
         kernel and the tensor-core products.  False if the step does not qualify."""
-        if norm is None:
+        if norm is None or self.conv is not None:
             return False
         if (ctx.T > FUSED_MAX_TOKENS and self.dtype == torch.bfloat16 and not _force_plain
                 and h.dtype == torch.float32 and h.is_contiguous()):
@@ -244,7 +368,8 @@ class Attention(Part):
 
     def attend(self, q, o, ctx, kv):
         run_attention(q, o, ctx, kv, self.nh, self.nkv, self.hd, self.scale, self.window,
-                      self.dtype, self.sink)
+                      self.dtype, self.sink, vd=self.vd, bias=self.bias,
+                      bias_edges=self.bias_edges)
 
     def weight_bytes(self):
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()

@@ -14,6 +14,9 @@ mixer            ``forward(x[T, H], ctx, cache) -> y[T, H]`` (any float dtype);
 feed_forward     ``forward(x[T, H], ctx) -> y[T, H]``
 position         used by a mixer; ``rotate_and_store(qkv, ctx, kv_view, ...)``
 head             ``forward(n[R, H], ctx) -> logits[R, V] float32``
+shift            ``forward(h[T, H] float32, norm, ctx, state) -> x[T, H]``: the normed rows,
+                 each blended with the row of the token before it
+
 ===============  =============================================================
 
 Every part class also has ``weight_specs(params, hidden_size)``: a dict from a
@@ -34,7 +37,8 @@ import torch
 from ..config.spec import PartSpec
 from ..weights.loader import WeightSpec
 
-_KINDS = ("embedding", "norm", "mixer", "feed_forward", "position", "head", "arrangement")
+_KINDS = ("embedding", "norm", "mixer", "feed_forward", "position", "head", "arrangement",
+          "shift")
 _REGISTRY: Dict[str, Dict[str, Any]] = {k: {} for k in _KINDS}
 
 
@@ -95,7 +99,8 @@ class LayerCache:
 
     kv: Optional[Any] = None          # cretif_b200.cache.KVView
     state: Optional[torch.Tensor] = None   # [max_slots, *shape]
-    writes: bool = True               # False: the visit borrows another visit's cache
+    writes: bool = True               # False: the visit borrows another visit's keys and values
+    shift_state: Optional[torch.Tensor] = None   # [max_slots, H]: the branch's shift, if any
 
 
 class Part:

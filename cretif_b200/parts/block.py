@@ -8,7 +8,8 @@ after the feed-forward (src/model.cu:961-968, 1006-1018).  ``layer.branches`` is
 ordered list of the layer's branches (role, part, norm before it, norm after it) and
 ``caches[k]`` is what branch ``k`` keeps between steps (or ``None``).
 
-``residual``: one branch after the other, ``h += post_norm(part(norm(h)))`` each.  With a
+``residual``: one branch after the other, ``h += post_norm(part(shift(norm(h))))`` each (a
+shift, where a branch has one, blends each normed row with the row of the token before it).  With a
 mixer and a feed-forward behind a norm each this is the reference's block.  A branch without
 a norm hands its part the stream itself (converted to the part's compute type); a norm after
 the part that offers ``add_into(h, y)`` norms the part's output and adds it to the stream in
@@ -52,13 +53,21 @@ def run_residual(layer, h, pending, ctx, caches):
     for branch, cache in zip(layer.branches, caches):
         part = branch.part
         if (pending is None and branch.norm is not None and branch.post_norm is None
+                and getattr(branch, "shift", None) is None
                 and hasattr(part, "forward_from_residual")):
             took = (part.forward_from_residual(h, branch.norm, ctx, cache)
                     if branch.role == "mixer" else part.forward_from_residual(h, branch.norm, ctx))
             if took:
                 lowp = None
                 continue
-        if branch.norm is not None:
+        if getattr(branch, "shift", None) is not None:
+            # norm and blend with the row of the token before, from the stream itself
+            if pending is not None:
+                h.add_(pending)
+                pending = None
+            lowp = None
+            x = branch.shift.forward(h, branch.norm, ctx, cache.shift_state)
+        elif branch.norm is not None:
             x = branch.norm.forward(h, pending)              # h += pending; x = norm(h)
             if pending is not None:
                 lowp = None

@@ -1,0 +1,94 @@
+"""Routed experts: a feed-forward made of many small gated feed-forwards, of which every token
+uses a few.
+
+A router scores the experts per token, ``s = sigmoid(W_router x)`` in 32-bit; the ``top``
+experts with the largest scores are chosen and weighted by their scores as they are
+(``renormalize`` divides them by their sum).  An expert is ``down(silu(gate x) ⊙ up x)`` without
+biases.  ``weight_on`` says where the weight enters: ``"input"`` (the expert sees ``s · x``) or
+``"output"`` (its result is scaled).  The output is the sum over the token's experts.
+
+The step's (token, choice) pairs are sorted by expert on the device and each expert's rows
+are one slice of two grouped products (csrc/moe.cu): gate|up with the activation — and the
+weight, when it scales the input: the products are linear, so it is applied to the 32-bit sums —
+in its epilogue, then down; the choices are summed in their order.  The grid of every launch is
+fixed by the step's size alone, so steps can be captured as CUDA graphs.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from ..weights.loader import WeightSpec
+from .base import Part, register_part
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(Part):
+    """params: ``num_experts``, ``top``, ``intermediate_size`` (of one expert), ``weight_on``
+    ("input" | "output"), ``renormalize`` (default False), ``names``: ``router`` and the
+    patterns ``gate``, ``up``, ``down`` with ``{e}`` for the expert's number."""
+
+    graph_safe = True
+
+    def __init__(self, params, hidden_size, dtype, device):
+        super().__init__(params, hidden_size, dtype, device)
+        self.E = int(params["num_experts"])
+        self.top = int(params["top"])
+        self.inter = int(params["intermediate_size"])
+        self.weight_on = params.get("weight_on", "output")
+        self.renorm = bool(params.get("renormalize", False))
+        if self.weight_on not in ("input", "output"):
+            raise ValueError(f"routed_experts: weight_on must be 'input' or 'output', got "
+                             f"{self.weight_on!r}")
+        if not 0 < self.top <= self.E or self.E > 256:
+            raise ValueError(f"routed_experts: {self.top} of {self.E} experts (at most 256) "
+                             "cannot be chosen")
+        if params.get("activation", "silu") != "silu":
+            raise ValueError("routed_experts: only 'silu' has a kernel")
+
+    @classmethod
+    def weight_specs(cls, params, hidden_size):
+        E, F, n = params["num_experts"], params["intermediate_size"], params["names"]
+        out = {"router": (n["router"], WeightSpec((E, hidden_size), init=(0.0, 0.5)))}
+        for e in range(E):
+            out[f"gate{e}"] = (n["gate"].format(e=e), WeightSpec((F, hidden_size)))
+            out[f"up{e}"] = (n["up"].format(e=e), WeightSpec((F, hidden_size)))
+            out[f"down{e}"] = (n["down"].format(e=e), WeightSpec((hidden_size, F)))
+        return out
+
+    def load(self, tensors):
+        E = self.E
+        self.router = self._vector32(tensors["router"])            # 32-bit logits
+        # per expert [gate rows | up rows], all experts in one tensor
+        self.w_gu = self._matrix(torch.stack(
+            [torch.cat([tensors[f"gate{e}"], tensors[f"up{e}"]], dim=0) for e in range(E)]))
+        self.w_down = self._matrix(torch.stack([tensors[f"down{e}"] for e in range(E)]))
+
+    def forward(self, x, ctx):
+        T, H = x.shape
+        dev = x.device
+        P = T * self.top
+        ids = torch.empty((T, self.top), dtype=torch.int32, device=dev)
+        wts = torch.empty((T, self.top), dtype=torch.float32, device=dev)
+        ops.moe_route(x, self.router, self.top, ids, wts, renorm=self.renorm)
+        tiles = ops.moe_max_tiles(P, self.E)
+        idx = torch.empty(self.E + 1 + 2 * P + 2 * tiles, dtype=torch.int32, device=dev)
+        offsets, place, order = idx[:self.E + 1], idx[self.E + 1:self.E + 1 + P], \
+            idx[self.E + 1 + P:self.E + 1 + 2 * P]
+        tile_expert, tile_row0 = idx[self.E + 1 + 2 * P:self.E + 1 + 2 * P + tiles], \
+            idx[self.E + 1 + 2 * P + tiles:]
+        ops.moe_group(ids, self.E, offsets, place, order, tile_expert, tile_row0)
+        act = torch.empty((P, self.inter), dtype=self.dtype, device=dev)
+        on_input = self.weight_on == "input"
+        ops.moe_gemm(x, self.w_gu, act, self.top, 0, 1 if on_input else 0, wts, order, offsets,
+                     tile_expert, tile_row0)
+        rows = torch.empty((P, H), dtype=torch.float32, device=dev)
+        ops.moe_gemm(act, self.w_down, rows, self.top, 1, 0 if on_input else 2, wts, order,
+                     offsets, tile_expert, tile_row0)
+        y = torch.empty((T, H), dtype=torch.float32, device=dev)
+        ops.moe_combine(rows, place, self.top, y)
+        return y
+
+    def weight_bytes(self):
+        return ((self.w_gu.numel() + self.w_down.numel()) * self.w_down.element_size()
+                + 4 * self.router.numel())

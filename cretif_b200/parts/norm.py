@@ -62,3 +62,51 @@ class RMSNorm(Part):
 
     def weight_bytes(self):
         return self.weight.numel() * 4
+
+
+@register_part("norm", "dynamic_tanh")
+class DynamicTanh(Part):
+    """A norm without statistics: ``tanh(alpha x) * w + b`` element by element, with one learned
+    scalar ``alpha``.  params: ``name`` (the weight; the offset and the scalar are stored beside
+    it as ``<name>.b`` and ``<name>.alpha``); ``gain`` (optional: name of a per-channel factor
+    on the result, a layer scale).  It has ``forward`` and ``add_into`` like the RMS norm, and
+    offers ``pointwise_params()``: a promise that every element is normed on its own, so that a
+    kernel may apply the norm to single rows wherever it reads them."""
+
+    graph_safe = True
+
+    @classmethod
+    def weight_specs(cls, params, hidden_size):
+        n = params["name"]
+        out = {"weight": (n, WeightSpec((hidden_size,), init=(1.0, 0.1))),
+               "bias": (n + ".b", WeightSpec((hidden_size,), init=(0.0, 0.1))),
+               "alpha": (n + ".alpha", WeightSpec((), init=(0.7, 0.1)))}
+        if params.get("gain"):
+            out["gain"] = (params["gain"], WeightSpec((hidden_size,), init=(0.5, 0.1)))
+        return out
+
+    def load(self, tensors):
+        self.weight = self._vector32(tensors["weight"])
+        self.bias = self._vector32(tensors["bias"])
+        self.alpha = self._vector32(tensors["alpha"].reshape(1))
+        self.gain = self._vector32(tensors["gain"]) if "gain" in tensors else None
+
+    def pointwise_params(self):
+        """(weight, bias, alpha) when nothing else is applied (no gain), else None."""
+        return None if self.gain is not None else (self.weight, self.bias, self.alpha)
+
+    def forward(self, h, delta=None, rows=None, write_h=True):
+        R = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((R, h.shape[1]), dtype=self.dtype, device=h.device)
+        ops.dyt_rows(h, delta, self.weight, self.bias, self.alpha, out, gain=self.gain, rows=rows,
+                     write_h=write_h)
+        return out
+
+    def add_into(self, h, y, emit: bool = False):
+        """``h += norm(y)`` in one 32-bit kernel.  Nothing is returned: the next reader of the
+        stream stands behind a norm of its own."""
+        ops.dyt_add(h, y, self.weight, self.bias, self.alpha, gain=self.gain)
+        return None
+
+    def weight_bytes(self):
+        return 4 * (2 + (self.gain is not None)) * self.weight.numel() + 4

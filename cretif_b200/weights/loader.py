@@ -29,12 +29,22 @@ class WeightSpec:
     """What a part expects of one tensor.
 
     ``init`` is ``(mean, std)`` of the normal distribution used by the
-    random-weights mode; ``integer`` marks index tables.
+    random-weights mode; ``integer`` marks index tables.  ``free`` lists the axes
+    whose size the checkpoint decides (a table's number of rows, a low rank): the
+    part reads it from the tensor it is handed, and ``shape`` there is only what the
+    random-weights mode draws.
     """
 
     shape: Tuple[int, ...]
     init: Tuple[float, float] = (0.0, 0.02)
     integer: bool = False
+    free: Tuple[int, ...] = ()
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(
+            a == b or (i in self.free and a > 0)
+            for i, (a, b) in enumerate(zip(shape, self.shape)))
 
 
 def _normalise_dtype(t: torch.Tensor) -> torch.Tensor:
@@ -69,8 +79,9 @@ def load_weights(model_dir: str, manifest: Dict[str, WeightSpec],
     for path, names in by_file.items():
         for name, t in read_tensors(path, names).items():
             spec = manifest[name]
-            if tuple(t.shape) != tuple(spec.shape):
-                wrong.append(f"{name}: expected {list(spec.shape)}, file has {list(t.shape)}")
+            if not spec.fits(t.shape):
+                want = [("any" if i in spec.free else n) for i, n in enumerate(spec.shape)]
+                wrong.append(f"{name}: expected {want}, file has {list(t.shape)}")
                 continue
             if spec.integer == t.dtype.is_floating_point:
                 wrong.append(f"{name}: expected {'an integer' if spec.integer else 'a floating'} "
