@@ -22,7 +22,8 @@ static int launch_dm(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
                      const int* table, int table_stride, const int* tok_pos, const int* tok_seq,
                      const int* seq_slot, int nh, int nkv, float scale_log2, int window,
                      float* part_o, float* part_ml, void* out, int ldo, int* counters,
-                     unsigned int* fault, dim3 grid, cudaStream_t st, const float* sink) {
+                     unsigned int* fault, dim3 grid, cudaStream_t st, const float* sink,
+                     DistanceBias bias) {
   // Few CTAs (at most two per SM) walk many tiles each: a deeper ring keeps more of the cache
   // in flight per CTA, as long as two CTAs still fit an SM.
   static int sm_count = 0;
@@ -68,7 +69,7 @@ static int launch_dm(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
   cudaError_t e = cudaLaunchKernelEx(
       &cfg, attn_decode_mma_kernel<HD16, CLUSTER>, mk, mv, (const __nv_bfloat16*)q, ldq, table,
       table_stride, tok_pos, tok_seq, seq_slot, nh, nkv, scale_log2, window, part_o, part_ml,
-      (__nv_bfloat16*)out, ldo, counters, fault, g_dm_stamps, n_stages, sink);
+      (__nv_bfloat16*)out, ldo, counters, fault, g_dm_stamps, n_stages, sink, bias);
   return e == cudaSuccess ? launch_status() : (int)e;
 }
 
@@ -102,7 +103,27 @@ extern "C" int cretif_attn_decode_mma_sink(const void* q, int ldq, void* out, in
                                            int n_splits, float* part_o, float* part_ml,
                                            int* counters, const float* sink, unsigned int* fault,
                                            void* stream) {
+  return cretif_attn_decode_mma_bias(q, ldq, out, ldo, kc, vc, n_blocks, table, table_stride,
+                                     tok_pos, tok_seq, seq_slot, nh, nkv, hd, scale, window, bt, B,
+                                     n_splits, part_o, part_ml, counters, sink, nullptr, nullptr,
+                                     0, fault, stream);
+}
+
+// bias_near [nh, n_far], bias_far [nh] (float32, times log2 e; both null for none): added to the
+// scaled score of the key n positions back, bias_near[h, n] for n < n_far, bias_far[h] beyond.
+extern "C" int cretif_attn_decode_mma_bias(const void* q, int ldq, void* out, int ldo,
+                                           const void* kc, const void* vc, long long n_blocks,
+                                           const int* table, int table_stride, const int* tok_pos,
+                                           const int* tok_seq, const int* seq_slot, int nh, int nkv,
+                                           int hd, float scale, int window, int bt, int B,
+                                           int n_splits, float* part_o, float* part_ml,
+                                           int* counters, const float* sink,
+                                           const float* bias_near, const float* bias_far,
+                                           int n_far, unsigned int* fault, void* stream) {
   if (B <= 0) return kOk;
+  if ((bias_near != nullptr) != (bias_far != nullptr) || (bias_near && n_far < 1))
+    return kBadArgument;
+  const DistanceBias bias{bias_near, bias_far, n_far};
   if (nh <= 0 || nkv <= 0 || nh % nkv || nh / nkv > 8 || hd % 16 || hd < 16 || hd > 128 ||
       bt != kDmTile || n_splits <= 0 || n_splits > kDmTile || nkv > 65535 || B > 65535 ||
       window < 0 || ldq % 2)
@@ -124,10 +145,10 @@ extern "C" int cretif_attn_decode_mma_sink(const void* q, int ldq, void* out, in
     return cluster                                                                            \
                ? launch_dm<N, true>(mk, mv, q, ldq, table, table_stride, tok_pos, tok_seq,    \
                                     seq_slot, nh, nkv, scale_log2, window, part_o, part_ml,   \
-                                    out, ldo, counters, fault, grid, st, sink)                \
+                                    out, ldo, counters, fault, grid, st, sink, bias)          \
                : launch_dm<N, false>(mk, mv, q, ldq, table, table_stride, tok_pos, tok_seq,   \
                                      seq_slot, nh, nkv, scale_log2, window, part_o, part_ml,  \
-                                     out, ldo, counters, fault, grid, st, sink)
+                                     out, ldo, counters, fault, grid, st, sink, bias)
   switch (hd / 16) {
     CRETIF_DM(1); CRETIF_DM(2); CRETIF_DM(3); CRETIF_DM(4);
     CRETIF_DM(5); CRETIF_DM(6); CRETIF_DM(7); CRETIF_DM(8);

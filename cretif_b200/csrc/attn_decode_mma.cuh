@@ -92,6 +92,14 @@ __host__ __device__ constexpr size_t dm_mrg_floats() {
   return mrg > wts ? mrg : wts;
 }
 
+// A bias by distance: near [heads, n_far] and far [heads] (float32, times log2 e) are added to
+// the scaled score of the key n positions back, near[h, n] for n < n_far, far[h] beyond.
+struct DistanceBias {
+  const float* near_;
+  const float* far_;
+  int n_far;
+};
+
 template <int HD16, bool CLUSTER = false>
 __device__ __forceinline__ void attn_decode_mma_item(
     unsigned char* smem, const CUtensorMap* map_k, const CUtensorMap* map_v,
@@ -101,7 +109,8 @@ __device__ __forceinline__ void attn_decode_mma_item(
     float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
     int ldo, int* __restrict__ counters, unsigned int* __restrict__ fault, int split,
     int n_splits, int kvh, int b, uint32_t& it_base, unsigned long long* stamps = nullptr,
-    int n_stages = kDmStages, const float* __restrict__ sink = nullptr) {
+    int n_stages = kDmStages, const float* __restrict__ sink = nullptr,
+    DistanceBias bias = DistanceBias{nullptr, nullptr, 0}) {
   // sink (may be null): one number per query head; exp(sink) joins the denominator of that
   // head's softmax where the ranges are merged, with no key and no value.
   constexpr int hd = HD16 * 16;
@@ -265,7 +274,13 @@ __device__ __forceinline__ void attn_decode_mma_item(
         for (int e = 0; e < 2; ++e) {
           const int key = key0 + n * 8 + 2 * c + e;
           const bool valid = key <= pos && key >= first_key;
-          t4[n * 2 + e] = valid ? sacc[n][e] * scale_log2 : -INFINITY;
+          float sv = sacc[n][e] * scale_log2;
+          if (bias.near_ && valid && r < g) {
+            const int head = kvh * g + r, dist = pos - key;
+            sv += dist >= bias.n_far ? __ldg(bias.far_ + head)
+                                     : __ldg(bias.near_ + (size_t)head * bias.n_far + dist);
+          }
+          t4[n * 2 + e] = valid ? sv : -INFINITY;
         }
       float mx = fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3]));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -514,7 +529,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
                        int window, float* __restrict__ part_o, float* __restrict__ part_ml,
                        __nv_bfloat16* __restrict__ out, int ldo, int* __restrict__ counters,
                        unsigned int* __restrict__ fault, unsigned long long* stamps,
-                       int n_stages, const float* __restrict__ sink) {
+                       int n_stages, const float* __restrict__ sink, DistanceBias bias) {
   extern __shared__ unsigned char smem_raw[];
   if (kStamps && stamps && blockIdx.x + blockIdx.y + blockIdx.z == 0 && threadIdx.x == 0) {
     unsigned long long t;
@@ -530,7 +545,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k,
   attn_decode_mma_item<HD16, CLUSTER>(smem, &map_k, &map_v, q, ldq, table, table_stride, tok_pos,
                                       tok_seq, seq_slot, nh, nkv, scale_log2, window, part_o,
                                       part_ml, out, ldo, counters, fault, blockIdx.x, gridDim.x,
-                                      blockIdx.y, blockIdx.z, it_base, stamps, n_stages, sink);
+                                      blockIdx.y, blockIdx.z, it_base, stamps, n_stages, sink,
+                                      bias);
 }
 
 }  // namespace cretif

@@ -96,7 +96,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                        const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale_log2,
                        int window, unsigned int* __restrict__ fault,
-                       unsigned long long* stamps, const float* __restrict__ sink) {
+                       unsigned long long* stamps, const float* __restrict__ sink,
+                       const float* __restrict__ bias_near, const float* __restrict__ bias_far,
+                       int n_far) {
+  // bias_near [nh, n_far], bias_far [nh] (both times log2 e, may be null): what is added to the
+  // scaled score of the key n positions back, for n < n_far and for every n beyond
   extern __shared__ unsigned char smem_raw[];
   // Tuning aid: with a buffer given, the first CTA (the heaviest tile) notes the times at
   // which its MMA thread and one softmax thread pass the phases of steps 0 .. 7:
@@ -299,6 +303,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       if (warp == 2) stamp(jj, 6);
     };
     float alpha_before = 0.f;
+    // the head's bias by distance, in shared memory behind the exchange buffers
+    const float* bias_s = reinterpret_cast<const float*>(smem + L.xch + 4 * kPfBQ * 4);
+    const float far_b = bias_near ? bias_far[h] : 0.f;
+    if (bias_near) {
+      float* dst = reinterpret_cast<float*>(smem + L.xch + 4 * kPfBQ * 4);
+      for (int i = (int)threadIdx.x - 64; i < n_far; i += 256) dst[i] = bias_near[(size_t)h * n_far + i];
+      asm volatile("bar.sync 5, 256;" ::: "memory");
+    }
+    // with a bias the scores are scaled and biased first and the softmax then takes them as they are
+    const float sc_log2 = bias_near ? 1.0f : scale_log2;
     for (int j = 0; j < n_tiles; ++j) {
       if (warp == 2) stamp(j, 0);
       unsigned char* prow = prow0 + (defer ? (j & 1) * kPBytes : 0);
@@ -327,6 +341,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
         for (int c = 0; c < 64; ++c) t[c] = __uint_as_float(c < 32 ? sa[c] : sb[c - 32]);
       }
+      if (bias_near) {
+        // a step whose every key lies n_far or more behind the tile's first row adds one number
+        if (pos_first - (key0 + 63) >= n_far) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) t[c] = fmaf(t[c], scale_log2, far_b);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            const int n = q_pos - (key0 + c);
+            const float bv = n >= n_far ? far_b : bias_s[max(n, 0)];
+            t[c] = fmaf(t[c], scale_log2, bv);          // a masked score stays -inf
+          }
+        }
+      }
       // (three-input maxima and two-wide float operations halve the instructions of the
       // loops below: what bounds a step is how many instructions its eight warps can issue)
       float mx4[4] = {t[0], t[1], t[2], t[3]};
@@ -340,7 +368,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       mx4[0] = max3(mx4[0], t[60], t[61]);
       mx4[1] = max3(mx4[1], t[62], t[63]);
       // the scale is positive, so the largest raw score is the largest scaled one
-      const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const float mine = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc_log2;
       float* xb = xch + (j & 1) * 256;        // double-buffered: one barrier per step
       xb[half * 128 + row] = mine;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
@@ -352,7 +380,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const float neg_m = (m_new == -INFINITY) ? 0.f : -m_new;
       float2 sum4[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
       uint32_t packed[32];
-      const float2 scale2 = make_float2(scale_log2, scale_log2), neg2 = make_float2(neg_m, neg_m);
+      const float2 scale2 = make_float2(sc_log2, sc_log2), neg2 = make_float2(neg_m, neg_m);
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
         const float2 x = __ffma2_rn(make_float2(t[c], t[c + 1]), scale2, neg2);
@@ -864,7 +892,25 @@ extern "C" int cretif_attn_prefill_tc_sink(const void* qkv, int ldq, int T, void
                                            float scale, int window, int bt, int B, int max_new,
                                            const float* sink, unsigned int* fault,
                                            void* stream) {
+  return cretif_attn_prefill_tc_bias(qkv, ldq, T, out, ldo, kc, vc, n_blocks, table, table_stride,
+                                     cu_seqlens, seq_start, seq_slot, nh, nkv, hd, scale, window,
+                                     bt, B, max_new, sink, nullptr, nullptr, 0, fault, stream);
+}
+
+// bias_near [nh, n_far] and bias_far [nh] (float32, times log2 e; both null for none): added to
+// the scaled score of the key n positions back, bias_near[h, n] for n < n_far, bias_far[h] beyond.
+extern "C" int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void* out, int ldo,
+                                           const void* kc, const void* vc, long long n_blocks,
+                                           const int* table, int table_stride,
+                                           const int* cu_seqlens, const int* seq_start,
+                                           const int* seq_slot, int nh, int nkv, int hd,
+                                           float scale, int window, int bt, int B, int max_new,
+                                           const float* sink, const float* bias_near,
+                                           const float* bias_far, int n_far, unsigned int* fault,
+                                           void* stream) {
   if (B <= 0 || T <= 0) return kOk;
+  if ((bias_near != nullptr) != (bias_far != nullptr) || (bias_near && (n_far < 1 || n_far > 8192)))
+    return kBadArgument;
   if (nh <= 0 || nkv <= 0 || nh % nkv || hd % 16 || hd < 16 || hd > 128 || bt != kPfBlk ||
       window < 0 || !(scale > 0.f) || max_new <= 0 || B > 65535 || ldq % 8 || ldo % 8 ||
       (max_new + kPfBQ - 1) / kPfBQ > 65535)
@@ -883,7 +929,9 @@ extern "C" int cretif_attn_prefill_tc_sink(const void* qkv, int ldq, int T, void
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nh, B, (max_new + kPfBQ - 1) / kPfBQ);
   cfg.blockDim = dim3(kPfThreads);
-  cfg.dynamicSmemBytes = L.total;
+  const int smem_bytes = L.total + (bias_near ? ((n_far * 4 + 15) & ~15) : 0);
+  if (smem_bytes > 227 * 1024) return kBadArgument;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -904,7 +952,8 @@ extern "C" int cretif_attn_prefill_tc_sink(const void* qkv, int ldq, int T, void
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const bool rows_ok = g_pf_pairing != 0 && hd <= 64 && window == 0 && items <= 65535 && !sink;
+  const bool rows_ok = g_pf_pairing != 0 && hd <= 64 && window == 0 && items <= 65535 && !sink &&
+                       !bias_near;
   const bool paired = rows_ok && (g_pf_pairing == 1 ||
                                   (g_pf_pairing < 0 && 5 * pairs * nkv * B >= 7LL * sm_count));
   if (rows_ok) {
@@ -928,27 +977,29 @@ extern "C" int cretif_attn_prefill_tc_sink(const void* qkv, int ldq, int T, void
   count_variant(kVarPrefillAttn);
   if (hd <= 64) {
     static int configured = 0;
-    if (L.total > configured) {
+    if (smem_bytes > configured) {
       e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
       if (e != cudaSuccess) return (int)e;
-      configured = L.total;
+      configured = smem_bytes;
     }
     e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel<64>, map_q, map_k, map_v,
                            (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
-                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps, sink);
+                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps, sink,
+                           bias_near, bias_far, n_far);
     if (e != cudaSuccess) return (int)e;
   } else {
     static int configured = 0;
-    if (L.total > configured) {
+    if (smem_bytes > configured) {
       e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, L.total);
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
       if (e != cudaSuccess) return (int)e;
-      configured = L.total;
+      configured = smem_bytes;
     }
     e = cudaLaunchKernelEx(&cfg, attn_prefill_tc_kernel<128>, map_q, map_k, map_v,
                            (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
-                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps, sink);
+                           seq_slot, nh, nkv, hd, scale_log2, window, fault, g_pf_stamps, sink,
+                           bias_near, bias_far, n_far);
     if (e != cudaSuccess) return (int)e;
   }
   return launch_status();

@@ -763,9 +763,18 @@ def decode_plan(B: int, nkv: int, max_context: int, device, hd: int = 64):
 
 def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv: int, hd: int,
                 scale: float, window: int, block_tokens: int, n_splits: int, fault,
-                cluster: bool = False, sink=None) -> None:
+                cluster: bool = False, sink=None, bias_near=None, bias_far=None) -> None:
     """``sink`` (float32 [heads], optional; tensor-core kernel only): exp(sink_h) joins head h's
-    softmax denominator."""
+    softmax denominator.  ``bias_near`` [heads, n_far] with ``bias_far`` [heads] (float32, times
+    log2 e; tensor-core kernel only): what the key n positions back adds to its scaled score."""
+    n_far = 0
+    if bias_near is not None:
+        _need(bias_near, "bias_near", torch.float32, 2); _need(bias_far, "bias_far", torch.float32, 1)
+        n_far = bias_near.shape[1]
+        if (bias_near.shape[0] != nh or bias_far.numel() != nh or not bias_near.is_contiguous()
+                or not bias_far.is_contiguous() or hd > 128 or _decode_simt_only):
+            raise KernelError("attn_decode: the bias is [heads, distances] with one far value "
+                              "per head, and needs head_dim <= 128")
     if sink is not None:
         _need(sink, "sink", torch.float32, 1)
         if sink.numel() != nh or hd > 128 or _decode_simt_only:
@@ -782,22 +791,23 @@ def attn_decode(q, out, kc, vc, table, tok_pos, tok_seq, seq_slot, nh: int, nkv:
         if hd > 128 or _decode_simt_only or n_splits > CLUSTER_MAX_RANGES:
             raise KernelError("attn_decode: the cluster merge takes head sizes up to 128 and at "
                               f"most {CLUSTER_MAX_RANGES} ranges")
-        _check(lib().cretif_attn_decode_mma_sink(
+        _check(lib().cretif_attn_decode_mma_bias(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc),
             ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
             _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
-            None, None, None, _p(sink), _p(fault), _stream()), "attn_decode_mma")
+            None, None, None, _p(sink), _p(bias_near), _p(bias_far), n_far, _p(fault), _stream()),
+            "attn_decode_mma")
         return
     part_o = torch.empty((B, nh, n_splits, hd), dtype=torch.float32, device=q.device)
     part_ml = torch.empty((B, nh, n_splits, 2), dtype=torch.float32, device=q.device)
     counters = _decode_counters(q.device, B * nkv)
     if hd <= 128 and not _decode_simt_only:
-        _check(lib().cretif_attn_decode_mma_sink(
+        _check(lib().cretif_attn_decode_mma_bias(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc),
             ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(tok_pos), _p(tok_seq),
             _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, n_splits,
-            _p(part_o), _p(part_ml), _p(counters), _p(sink), _p(fault), _stream()),
-            "attn_decode_mma")
+            _p(part_o), _p(part_ml), _p(counters), _p(sink), _p(bias_near), _p(bias_far), n_far,
+            _p(fault), _stream()), "attn_decode_mma")
         return
     _check(lib().cretif_attn_decode(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(kc), _p(vc), _p(table),
@@ -1016,9 +1026,19 @@ def attn_prefill_supported(hd: int, block_tokens: int) -> bool:
 
 def attn_prefill(qkv, out, kc, vc, table, cu_seqlens, seq_start, seq_slot, nh: int, nkv: int,
                  hd: int, scale: float, window: int, block_tokens: int, B: int, max_new: int,
-                 fault, sink=None) -> None:
+                 fault, sink=None, bias_near=None, bias_far=None) -> None:
     """Causal attention of whole prompts; ``qkv`` rows start with the query heads.  ``sink``
-    (float32 [heads], optional): exp(sink_h) joins head h's softmax denominator."""
+    (float32 [heads], optional): exp(sink_h) joins head h's softmax denominator.  ``bias_near``
+    [heads, n_far] with ``bias_far`` [heads] (float32, times log2 e): what the key n positions
+    back adds to its scaled score, for n < n_far and for every n beyond."""
+    n_far = 0
+    if bias_near is not None:
+        _need(bias_near, "bias_near", torch.float32, 2); _need(bias_far, "bias_far", torch.float32, 1)
+        n_far = bias_near.shape[1]
+        if (bias_near.shape[0] != nh or bias_far.numel() != nh or not bias_near.is_contiguous()
+                or not bias_far.is_contiguous()):
+            raise KernelError("attn_prefill: the bias is [heads, distances] with one far value "
+                              "per head")
     if sink is not None:
         _need(sink, "sink", torch.float32, 1)
         if sink.numel() != nh:
@@ -1028,8 +1048,8 @@ def attn_prefill(qkv, out, kc, vc, table, cu_seqlens, seq_start, seq_slot, nh: i
     if (tuple(kc.shape[1:]) != (nkv, block_tokens, hd) or not kc.is_contiguous()
             or not vc.is_contiguous()):
         raise KernelError("attn_prefill: cache must be contiguous [blocks, kv_heads, 64, head_dim]")
-    _check(lib().cretif_attn_prefill_tc_sink(
+    _check(lib().cretif_attn_prefill_tc_bias(
         _p(qkv), _rows(qkv, "qkv"), qkv.shape[0], _p(out), _rows(out, "out"), _p(kc), _p(vc),
         ctypes.c_longlong(kc.shape[0]), _p(table), table.stride(0), _p(cu_seqlens), _p(seq_start),
         _p(seq_slot), nh, nkv, hd, ctypes.c_float(scale), window, block_tokens, B, max_new,
-        _p(sink), _p(fault), _stream()), "attn_prefill_tc")
+        _p(sink), _p(bias_near), _p(bias_far), n_far, _p(fault), _stream()), "attn_prefill_tc")

@@ -78,19 +78,25 @@ def distance_edges(rows: int, far: float):
     return edges.astype(np.int32)
 
 
+# The tensor-core kernels take a bias by distance as a dense table of its first distances (up
+# to this many, in shared memory) plus one number for everything farther.
+FAST_BIAS_MAX_DISTANCES = 4096
+
+
 def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, vd=0, bias=None,
-                  bias_edges=None):
+                  bias_edges=None, bias_dense=None):
     """Causal (windowed) attention of the step's queries ``q`` [T, nh·hd] over the cache view
     ``kv`` into ``o``, with the kernel that fits the step: the decode kernels when every
     sequence brings one token, the prompt kernel otherwise, the plain kernel for float32 and
-    for whatever the fast ones do not take (a bias by distance, values of another size)."""
+    for whatever the fast ones do not take (values of another size than the keys, a bias whose
+    rows reach farther than the fast kernels' table).  ``bias`` [rows, heads] with
+    ``bias_edges`` is the bias by distance as the plain kernel takes it, ``bias_dense`` =
+    (near [heads, n_far], far [heads]), times log2 e, as the tensor-core kernels do."""
     vd = vd or hd
-    if bias is not None or vd != hd:
-        ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
-                      nh, nkv, hd, scale, window, kv.block_tokens, sink=sink, vd=vd, bias=bias,
-                      bias_edges=bias_edges)
-        return
-    if not _force_plain and dtype == torch.bfloat16 and (sink is None or hd <= 128):
+    fast = (not _force_plain and dtype == torch.bfloat16 and (sink is None or hd <= 128)
+            and vd == hd and (bias is None or (bias_dense is not None and hd <= 128)))
+    near, far = bias_dense if (bias is not None and bias_dense is not None) else (None, None)
+    if fast:
         if ctx.is_decode and ops.attn_decode_supported(hd, kv.block_tokens, min(nh // nkv, 8)) \
                 and (nh // nkv <= 8 or nkv == 1):
             # the kernel takes up to eight query heads per key/value head; more heads on ONE
@@ -102,15 +108,18 @@ def run_attention(q, o, ctx, kv, nh, nkv, hd, scale, window, dtype, sink=None, v
                 ops.attn_decode(q[:, h0 * hd:], o[:, h0 * hd:], kv.k, kv.v, kv.table,
                                 ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, n, nkv, hd, scale,
                                 window, kv.block_tokens, splits, ctx.fault, cluster,
-                                sink=None if sink is None else sink[h0:h0 + n])
+                                sink=None if sink is None else sink[h0:h0 + n],
+                                bias_near=None if near is None else near[h0:h0 + n],
+                                bias_far=None if far is None else far[h0:h0 + n])
             return
         if not ctx.is_decode and ops.attn_prefill_supported(hd, kv.block_tokens):
             ops.attn_prefill(q, o, kv.k, kv.v, kv.table, ctx.cu_seqlens, ctx.seq_start,
                              ctx.seq_slot, nh, nkv, hd, scale, window, kv.block_tokens, ctx.B,
-                             ctx.max_new, ctx.fault, sink=sink)
+                             ctx.max_new, ctx.fault, sink=sink, bias_near=near, bias_far=far)
             return
     ops.attn_simt(q, o, kv.k, kv.v, kv.table, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
-                  nh, nkv, hd, scale, window, kv.block_tokens, sink=sink)
+                  nh, nkv, hd, scale, window, kv.block_tokens, sink=sink, vd=vd, bias=bias,
+                  bias_edges=bias_edges)
 
 
 @register_part("mixer", "attention")
@@ -160,7 +169,7 @@ class Attention(Part):
         self.head_norm = params.get("head_norm")
         self.query_gain = params.get("query_gain")
         self.distance_bias = params.get("distance_bias")
-        self.bias = self.bias_edges = None
+        self.bias = self.bias_edges = self.bias_dense = None
         extras = [k for k in ("head_norm", "query_gain", "distance_bias") if params.get(k)] \
             + (["value_dim"] if self.vd != self.hd else []) + ([] if self.own_kv else ["own_kv"])
         if self.conv is None and extras:
@@ -221,8 +230,16 @@ class Attention(Part):
             self.conv_w = self._vector32(torch.cat(taps, dim=0))
         if self.distance_bias is not None:
             self.bias = self._vector32(tensors["rel"])
-            self.bias_edges = torch.from_numpy(distance_edges(
-                self.bias.shape[0], float(self.distance_bias["far"]))).to(self.device)
+            edges = distance_edges(self.bias.shape[0], float(self.distance_bias["far"]))
+            self.bias_edges = torch.from_numpy(edges).to(self.device)
+            n_far = int(edges[-1])              # from here on every distance is the last row
+            if 1 <= n_far <= FAST_BIAS_MAX_DISTANCES and self.dtype == torch.bfloat16:
+                import numpy as np
+                row_of = np.searchsorted(edges, np.arange(n_far), side="right") - 1
+                log2e = 1.4426950408889634
+                near = self.bias[torch.from_numpy(row_of).to(self.device)].t().contiguous()
+                self.bias_dense = ((near * log2e).contiguous(),
+                                   (self.bias[-1] * log2e).contiguous())
         if self.params.get("fixed_sink") is not None:
             self.sink = torch.full((self.nh,), float(self.params["fixed_sink"]),
                                    dtype=torch.float32, device=self.device)
@@ -369,7 +386,7 @@ class Attention(Part):
     def attend(self, q, o, ctx, kv):
         run_attention(q, o, ctx, kv, self.nh, self.nkv, self.hd, self.scale, self.window,
                       self.dtype, self.sink, vd=self.vd, bias=self.bias,
-                      bias_edges=self.bias_edges)
+                      bias_edges=self.bias_edges, bias_dense=self.bias_dense)
 
     def weight_bytes(self):
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()

@@ -279,6 +279,78 @@ def test_attention_with_distance_rows_other_value_size_and_one_added(H, G, d, e,
     assert (out.cpu().double() - want).abs().max() > 1e-2
 
 
+@pytest.mark.parametrize("H,G,d,rows,far", [(6, 1, 96, 32, 200), (8, 2, 64, 12, 40),
+                                            (4, 4, 128, 64, 500), (2, 1, 16, 7, 100),
+                                            (16, 2, 32, 2, 3), (3, 1, 80, 20, 1000)])
+def test_fast_attention_kernels_with_distance_rows(H, G, d, rows, far):
+    """The bfloat16 attention kernels the engine picks (prompt, a further portion, single
+    tokens) with the bias by distance and the added one, against the formula on the same rounded
+    inputs; a key at a row's first distance, or just before it, stands out in every query."""
+    from cretif_b200.csrc import ops
+    from cretif_b200.parts.attention import distance_edges, run_attention
+    from cretif_b200.parts.base import StepContext
+    g = torch.Generator().manual_seed(7)
+    S = 700
+    q = torch.randn(S, H, d, generator=g)
+    k = torch.randn(S, G, d, generator=g)
+    edges = distance_edges(rows, far)
+    for i in range(S):
+        n = int(edges[(i * 5) % rows]) - (i % 2)
+        if 0 <= n <= i:
+            k[i - n, :, 0] += 3.0
+            q[i, :, 0] += 2.0
+    q, k = q.bfloat16(), k.bfloat16()
+    v = torch.randn(S, G, d, generator=g).bfloat16()
+    rel = (torch.randn(rows, H, generator=g) * 3).bfloat16().float()
+    scale = 0.7 / d ** 0.5
+    want = plain.attention_scores_to_output(q.double(), k.double(), v.double(), scale,
+                                            rel.double(), far, torch.ones(S, dtype=torch.float64)
+                                            ).reshape(S, H * d)
+    kc, table = _cache_for(S, G, d, torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    t = table[0].cpu()
+    for p in range(S):
+        kc[t[p // 64], :, p % 64] = k[p].cuda()
+        vc[t[p // 64], :, p % 64] = v[p].cuda()
+
+    class KV:
+        pass
+    kv = KV()
+    kv.k, kv.v, kv.table, kv.block_tokens, kv.window = kc, vc, table, 64, 0
+    dev = torch.device("cuda")
+    i32 = dict(dtype=torch.int32, device=dev)
+    fault = torch.zeros(1, **i32)
+    n_far = int(edges[-1])
+    row_of = np.searchsorted(edges, np.arange(n_far), side="right") - 1
+    log2e = 1.4426950408889634
+    dense = ((rel[torch.from_numpy(row_of)].t() * log2e).contiguous().cuda(),
+             (rel[-1] * log2e).contiguous().cuda())
+    sink = torch.zeros(H, device=dev)
+
+    def ctx(T, first, decode):
+        return StepContext(T=T, B=1, tok_ids=torch.zeros(T, **i32),
+                           tok_pos=torch.arange(first, first + T, **i32),
+                           tok_seq=torch.zeros(T, **i32), seq_slot=torch.zeros(1, **i32),
+                           seq_start=torch.tensor([first], **i32),
+                           cu_seqlens=torch.tensor([0, T], **i32), is_decode=decode, max_new=T,
+                           max_context=1024 if decode else first + T, fault=fault,
+                           dtype=torch.bfloat16, device=dev)
+    before = ops.variant_counts()
+    for first, T, decode in ((0, S, False), (300, S - 300, False), (S - 1, 1, True),
+                             (150, 1, True), (int(edges[-1]), 1, True)):
+        out = torch.zeros(T, H * d, dtype=torch.bfloat16, device=dev)
+        run_attention(q[first:first + T].reshape(T, H * d).cuda(), out, ctx(T, first, decode), kv,
+                      H, G, d, scale, 0, torch.bfloat16, sink, bias=rel.cuda(),
+                      bias_edges=torch.from_numpy(edges).cuda(), bias_dense=dense)
+        err = (out.cpu().double() - want[first:first + T]).abs().max()
+        assert err <= 2e-2 * want.abs().max(), (first, T, decode, float(err))
+    after = ops.variant_counts()
+    assert after["prefill_attn"] - before["prefill_attn"] == 2          # the tensor-core kernels ran
+    assert (after["decode_cluster"] + after["decode_split"]
+            - before["decode_cluster"] - before["decode_split"]) == 3
+    assert int(fault.item()) == 0
+
+
 @pytest.mark.parametrize("H,d,e,R", [(2, 16, 16, 6), (3, 24, 24, 5), (1, 8, 8, 1), (3, 10, 10, 4),
                                      (2, 128, 128, 16), (1, 72, 130, 2), (1, 256, 32, 3),
                                      (4, 32, 32, 16)])
