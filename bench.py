@@ -21,13 +21,17 @@ fraction for each); ``prefill_b8`` and ``prefill_b64`` are steps over 8 and 64 p
 ``--dtype float32`` measures the true 32-bit path.
 Every weight plus the cache exceed the L2 cache, so no flush is needed between steps.
 
-    python bench.py --design rigozen [--design-size s|m] [--layers L]
+    python bench.py --design rigozen|losorax [--design-size s|m] [--layers L]
 
 measures another thing and leaves the line above as it is: prefill (1 and 8 prompts of 2,048
 tokens) and decode (batch 1, 8, 64 from a context of 2,048) of Rigozen models whose layers
 have real sizes -- all layers of one mixer (attention with keys as values, latent attention,
 gated delta rule) and a mixture -- beside the Llama model of the same width, feed-forward,
-heads and window, each with a roofline fraction (see design_bench).
+heads and window, each with a roofline fraction (see design_bench).  ``--design losorax`` does
+the same for Losorax models (all layers convolved attention with a dense or a routed
+feed-forward, all layers the generalized delta rule, and a mixture in which every second
+attention layer reads its neighbour's keys and values) beside Llama without a window and
+beside Rigozen's delta-rule layers.
 """
 from __future__ import annotations
 
@@ -310,10 +314,52 @@ def run_e2e(engine, batch, steps, prompt_len):
 # rule's heads and sizes; the window of every attention layer (Llama's too).
 DESIGN_SIZES = {
     "s": dict(width=576, ff=1536, vocab=49152, heads=9, kv=3, dim=64, rank=128,
-              d_heads=9, d_dim=64, d_vdim=64, window=1024),
+              d_heads=9, d_dim=64, d_vdim=64, window=1024,
+              experts=8, top=2, expert_ff=384, decay_rank=32),
     "m": dict(width=2048, ff=8192, vocab=49152, heads=32, kv=8, dim=64, rank=128,
-              d_heads=16, d_dim=128, d_vdim=128, window=1024),
+              d_heads=16, d_dim=128, d_vdim=128, window=1024,
+              experts=32, top=4, expert_ff=1024, decay_rank=64),
 }
+
+
+def losorax_configs(z, layers):
+    """name -> config.json of the models --design losorax measures: the routed feed-forward
+    has half the dense one's active width (top x expert_ff), the attention has no window."""
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
+           "scale": z["dim"] ** -0.5, "conv": 4, "bias_max": 1024, "bias_rows": 32,
+           "q_temp": {"coef": 0.3, "every": 128}}
+    dlt = {"heads": z["d_heads"], "dim": z["d_dim"], "decay_rank": z["decay_rank"]}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"]}}
+
+    def losorax(order, mlp):
+        out = []
+        for i, k in enumerate(order):
+            if k == "attention_reader":
+                out.append({"type": "attention", "mixer": dict(att, kv_from=i - 1), "mlp": mlp})
+            else:
+                out.append({"type": k, "mixer": att if k == "attention" else dlt, "mlp": mlp})
+        return {"architecture": "Losorax", "vocab": z["vocab"], "width": z["width"],
+                "norm": {"eps": 1e-6}, "max_positions": CONTEXT, "layers": out}
+    mixed = (["attention", "attention_reader", "general_delta", "attention"] * layers)[:layers]
+    rz_delta = {"heads": z["d_heads"], "kv_heads": z["d_heads"], "dim": z["d_dim"],
+                "vdim": z["d_vdim"], "conv": 4}
+    return {
+        "llama": {"architectures": ["LlamaForCausalLM"], "hidden_size": z["width"],
+                  "num_hidden_layers": layers, "num_attention_heads": z["heads"],
+                  "num_key_value_heads": z["kv"], "head_dim": z["dim"],
+                  "intermediate_size": z["ff"], "vocab_size": z["vocab"],
+                  "rope_theta": 100000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+                  "max_position_embeddings": CONTEXT},
+        "rigozen delta": {"architecture": "Rigozen", "vocab": z["vocab"], "width": z["width"],
+                          "norm": {"eps": 1e-6}, "max_positions": CONTEXT,
+                          "layers": [{"type": "delta", "mixer": rz_delta, "mlp": dense}] * layers},
+        "losorax attention dense": losorax(["attention"] * layers, dense),
+        "losorax attention routed": losorax(["attention"] * layers, moe),
+        "losorax delta dense": losorax(["general_delta"] * layers, dense),
+        "losorax mixed routed": losorax(mixed, moe),
+    }
 
 
 def design_configs(z, layers):
@@ -362,8 +408,9 @@ def design_bench(args) -> int:
     pk = peaks()
     T, W, V = PROMPT_LEN, z["width"], z["vocab"]
     rows = {}
+    configs = losorax_configs(z, layers) if args.design == "losorax" else design_configs(z, layers)
     with ClockSampler() as clocks:
-        for name, cfg in design_configs(z, layers).items():
+        for name, cfg in configs.items():
             tmp = tempfile.mkdtemp(prefix="cretif_design_")
             try:
                 write_random_model(tmp, cfg, seed=99)
@@ -373,12 +420,31 @@ def design_bench(args) -> int:
                 shutil.rmtree(tmp, ignore_errors=True)
             wbytes = engine.model.weight_bytes()
             params = wbytes / (2 if args.dtype == "bfloat16" else 4)
-            window = z["window"]
+            window = z["window"] if "sliding_window" in cfg or cfg.get("architecture") == "Rigozen" \
+                else T
             kinds = ([l["type"] for l in cfg["layers"]] if "layers" in cfg
                      else ["llama"] * layers)
+            # routed experts: a token multiplies by `top` of them, a step reads those it uses
+            routed = [l["mlp"] for l in cfg.get("layers", [])
+                      if (l.get("mlp") or {}).get("kind") == "moe"]
+            expert_params = sum(3 * W * m["expert"]["ff"] * m["router"]["experts"] for m in routed)
+            active_params = params - expert_params + sum(
+                3 * W * m["expert"]["ff"] * m["router"]["top"] for m in routed)
+
+            def read_params(b):
+                return params - expert_params + sum(
+                    3 * W * m["expert"]["ff"] * min(m["router"]["experts"], b * m["router"]["top"])
+                    for m in routed)
+            # the embedding table is read a row at a time; an output matrix of its own is
+            # multiplied on the last rows only
+            untied = cfg.get("architecture") == "Losorax"
+            tables = V * W * (2 if untied else 1)
             attn_flops = kept = 0.0
-            for k in kinds:
-                if k == "delta":
+            for i, k in enumerate(kinds):
+                if k == "general_delta":
+                    attn_flops += T * z["d_heads"] * 8 * z["d_dim"] * z["d_dim"]
+                    kept += 2 * 4 * z["d_heads"] * z["d_dim"] * z["d_dim"]
+                elif k == "delta":
                     attn_flops += T * z["d_heads"] * 8 * z["d_dim"] * z["d_vdim"]
                     kept += 2 * 4 * z["d_heads"] * z["d_dim"] * z["d_vdim"]
                 else:
@@ -390,7 +456,7 @@ def design_bench(args) -> int:
             rec = {"layers": layers, "weight_bytes": wbytes}
             for b in (1, 8):
                 ms = run_prefill(engine, T, repeats=3, warmup=3, batch=b)
-                flops = b * (2 * T * (params - V * W) + 2 * V * W + attn_flops)
+                flops = b * (2 * T * (active_params - tables) + 2 * V * W + attn_flops)
                 rec[f"prefill_b{b}_ms"] = ms
                 rec[f"prefill_b{b}_tok_s"] = b * T / (ms * 1e-3)
                 rec[f"prefill_b{b}_frac_bf16"] = flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
@@ -399,13 +465,15 @@ def design_bench(args) -> int:
                                              seed=b)
                 rec[f"decode_b{b}_ms"] = ms
                 rec[f"decode_b{b}_tok_s"] = b / (ms * 1e-3)
-                rec[f"decode_b{b}_frac_hbm"] = ((wbytes + b * kept) / (ms * 1e-3) / 1e9
+                rbytes = (read_params(b) - (V * W if untied else 0)) \
+                    * (2 if args.dtype == "bfloat16" else 4)
+                rec[f"decode_b{b}_frac_hbm"] = ((rbytes + b * kept) / (ms * 1e-3) / 1e9
                                                 / pk["hbm_gbs"])
                 rec["launches_per_step"] = per_step
             rows[name] = rec
             del engine
             torch.cuda.empty_cache()
-    print(json.dumps({"design": "rigozen", "size": args.design_size, "sizes": z,
+    print(json.dumps({"design": args.design, "size": args.design_size, "sizes": z,
                       "dtype": args.dtype, "prompt_len": T, "data": "synthetic",
                       "weights": "random, seed 99", "peaks": pk, "models": rows,
                       "clocks": clocks.result}))
@@ -506,7 +574,7 @@ def main() -> int:
                     help="skip the per-kernel shares of the decode step")
     ap.add_argument("--unequal", action="store_true",
                     help="prompts of unequal lengths 256..2,048 instead of 2,048 each")
-    ap.add_argument("--design", default=None, choices=["rigozen"],
+    ap.add_argument("--design", default=None, choices=["rigozen", "losorax"],
                     help="measure this design at real layer sizes beside Llama at the same "
                          "sizes instead of the headline (another JSON line)")
     ap.add_argument("--design-size", default="m", choices=sorted(DESIGN_SIZES))

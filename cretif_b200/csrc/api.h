@@ -101,10 +101,13 @@ int cretif_conv_headnorm_kv_append(const float* proj, int ldp, const float* conv
 
 // The generalized delta rule (delta_rule.cu).  proj rows (float32): [r (H d) | k (H d) | v (H e) |
 // gate (H e) | a (H d) | w1 (R)]; prep rows: [u (H d) | b (H d) | w (H d)].
+// z rows: W2 tanh(w1) [H d] (the expanding product of the decay's low rank).
 int cretif_general_delta_prepare(const float* proj, int ldp, float* prep, int ldo,
-                                 const float* a_bias, const float* w2, const float* w0, int R,
+                                 const float* a_bias, const float* z, int ldz, const float* w0,
                                  int H, int d, int e, float unit_eps, float decay_scale, int T,
                                  void* stream);
+// out[t, j] = tanh(in[t * ld + j]), j < R, in the element type out_dt.
+int cretif_tanh_cols(const float* in, int ld, void* out, int out_dt, int R, int T, void* stream);
 int cretif_general_delta_recurrence(const float* proj, int ldp, const float* prep, int ldq,
                                     const float* gate, int ldg, float* state,
                                     long long state_stride, const int* cu_seqlens,
@@ -122,6 +125,10 @@ int cretif_moe_gemm(const void* A, int a_dt, int lda, const void* W, int w_dt, v
                     int N, int K, int top, int mode, int scale_at, const float* wts,
                     const int* order, const int* offsets, const int* tile_expert,
                     const int* tile_row0, int max_tiles, int use_mma, void* stream);
+int cretif_moe_gemv(const void* A, int a_dt, int lda, const void* W, int w_dt, void* C, int ldc,
+                    int N, int K, int top, int mode, int scale_at, const int* ids,
+                    const float* wts, int P, void* stream);
+// place may be null: the rows are in the pairs' own order.
 int cretif_moe_combine(const float* rows, int ld, const int* place, int top, float* y, int T,
                        int H, void* stream);
 

@@ -22,7 +22,8 @@ namespace {
 constexpr int kCvWarps = 8;
 constexpr int kCvMaxD = 512;
 
-template <typename T>
+// NCH: channels a lane keeps (head sizes up to 32 NCH)
+template <typename T, int NCH>
 __global__ void __launch_bounds__(kCvWarps * 32)
 conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
                                const float* __restrict__ conv_w, int taps,
@@ -59,10 +60,10 @@ conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
   const int n = (is_q || is_k) ? hd : vd;
   const int c0 = is_q ? unit * hd : is_k ? nh * hd + (unit - nh) * hd
                                          : (nh + nkv) * hd + (unit - nh - nkv) * vd;
-  float val[kCvMaxD / 32];
+  float val[NCH];
   float ss = 0.f;
 #pragma unroll
-  for (int m = 0; m < kCvMaxD / 32; ++m) {
+  for (int m = 0; m < NCH; ++m) {
     const int i = lane + 32 * m;
     val[m] = i < n ? conv(c0 + i) : 0.f;
     ss += val[m] * val[m];
@@ -76,7 +77,7 @@ conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
     if (gain_every > 0) f *= 1.0f + gain_coef * logf((float)((pos + 1) / gain_every + 1));
     T* q = q_out + (size_t)t * ldq + (size_t)unit * hd;
 #pragma unroll
-    for (int m = 0; m < kCvMaxD / 32; ++m) {
+    for (int m = 0; m < NCH; ++m) {
       const int i = lane + 32 * m;
       if (i < n) q[i] = from_float<T>(val[m] * f);
     }
@@ -91,7 +92,7 @@ conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
   const int kvh = is_k ? unit - nh : unit - nh - nkv;
   T* dst = (is_k ? kc : vc) + (((size_t)blk * nkv + kvh) * bt + (pos % bt)) * n;
 #pragma unroll
-  for (int m = 0; m < kCvMaxD / 32; ++m) {
+  for (int m = 0; m < NCH; ++m) {
     const int i = lane + 32 * m;
     if (i < n) dst[i] = from_float<T>(val[m] * f);
   }
@@ -117,17 +118,26 @@ extern "C" int cretif_conv_headnorm_kv_append(
   dim3 grid(T, (units + kCvWarps - 1) / kCvWarps);
   if (grid.y > 65535) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
+  const int widest = nkv > 0 && vd > hd ? vd : hd;
+#define CRETIF_CONV(TT, NCH)                                                                    \
+  conv_headnorm_kv_append_kernel<TT, NCH><<<grid, kCvWarps * 32, 0, st>>>(                       \
+      proj, ldp, conv_w, taps, conv_state, (size_t)state_stride, tok_pos, tok_seq, seq_slot,     \
+      seq_start, nh, nkv, hd, vd, eps, gain_coef, gain_every, (TT*)q_out, ldq, table,            \
+      table_stride, (TT*)kc, (TT*)vc, bt, write_cache, fault)
+#define CRETIF_CONV_T(TT)                                                                       \
+  do {                                                                                          \
+    if (widest <= 64) CRETIF_CONV(TT, 2);                                                        \
+    else if (widest <= 128) CRETIF_CONV(TT, 4);                                                  \
+    else if (widest <= 256) CRETIF_CONV(TT, 8);                                                  \
+    else CRETIF_CONV(TT, 16);                                                                    \
+  } while (0)
   if (dt == kF32)
-    conv_headnorm_kv_append_kernel<float><<<grid, kCvWarps * 32, 0, st>>>(
-        proj, ldp, conv_w, taps, conv_state, (size_t)state_stride, tok_pos, tok_seq, seq_slot,
-        seq_start, nh, nkv, hd, vd, eps, gain_coef, gain_every, (float*)q_out, ldq, table,
-        table_stride, (float*)kc, (float*)vc, bt, write_cache, fault);
+    CRETIF_CONV_T(float);
   else if (dt == kBF16)
-    conv_headnorm_kv_append_kernel<__nv_bfloat16><<<grid, kCvWarps * 32, 0, st>>>(
-        proj, ldp, conv_w, taps, conv_state, (size_t)state_stride, tok_pos, tok_seq, seq_slot,
-        seq_start, nh, nkv, hd, vd, eps, gain_coef, gain_every, (__nv_bfloat16*)q_out, ldq, table,
-        table_stride, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, bt, write_cache, fault);
+    CRETIF_CONV_T(__nv_bfloat16);
   else
     return kBadDType;
+#undef CRETIF_CONV_T
+#undef CRETIF_CONV
   return launch_status();
 }

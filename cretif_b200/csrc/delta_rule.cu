@@ -447,9 +447,9 @@ extern "C" int cretif_delta_recurrence(const float* prep, int ldp, const float* 
 // (The gated rule above is the case w = g, u = k, b = beta g k, v scaled by beta.)
 //
 // * general_delta_prepare (a warp per head of a token): u = k / sqrt(|k|^2 + unit_eps),
-//   b = sigmoid(a_proj + a_bias) * u, w = exp(-decay_scale * sigmoid(W2 tanh(w1) + w0)), where
-//   w1 is the token's low-rank projection (rank R, any size) and W2 [H d, R] expands it; the
-//   tanh of the R numbers is computed once per CTA into shared memory.
+//   b = sigmoid(a_proj + a_bias) * u, w = exp(-decay_scale * sigmoid(z + w0)), where
+//   z = W2 tanh(w1) comes from the library's matrix product: w1 is the token's low-rank
+//   projection (rank R, any size), tanh_cols applies the tanh and W2 [H d, R] expands it.
 // * general_delta_recurrence: the thread layout of delta_recurrence above -- a CTA per
 //   (sequence, head, slice of columns), P lanes a column, each lane a slice of the column's d
 //   rows in registers, a chunk's operands staged in shared memory by asynchronous copies a
@@ -462,30 +462,29 @@ namespace cretif {
 constexpr int kGenChunk = 8;
 
 // proj row: [r (H d) | k (H d) | v (H e) | gate (H e) | a (H d) | w1 (R)]
-// prep row: [u (H d) | b (H d) | w (H d)]
+// prep row: [u (H d) | b (H d) | w (H d)];  z row: W2 tanh(w1), [H d]
 __global__ void __launch_bounds__(kPrepWarps * 32)
 general_delta_prepare_kernel(const float* __restrict__ proj, int ldp, float* __restrict__ prep,
                              int ldo, const float* __restrict__ a_bias,
-                             const float* __restrict__ w2, const float* __restrict__ w0, int R,
+                             const float* __restrict__ z, int ldz, const float* __restrict__ w0,
                              int H, int d, int e, float unit_eps, float decay_scale) {
-  extern __shared__ float th[];                   // tanh of the token's low-rank projection
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const float* row = proj + (size_t)t * ldp;
-  const int w1_at = 3 * H * d + 2 * H * e;
-  for (int j = threadIdx.x; j < R; j += blockDim.x) th[j] = tanhf(row[w1_at + j]);
-  __syncthreads();
   const int h = blockIdx.y * kPrepWarps + warp;
   if (h >= H) return;
   float* out = prep + (size_t)t * ldo;
   const float* k = row + (size_t)H * d + (size_t)h * d;
   const float* a = row + (size_t)2 * H * d + (size_t)2 * H * e + (size_t)h * d;
-  float kv[kPrepMaxD / 32];
+  const float* zrow = z + (size_t)t * ldz + (size_t)h * d;
+  float kv[kPrepMaxD / 32], av[kPrepMaxD / 32], zv[kPrepMaxD / 32];
   float ss = 0.f;
 #pragma unroll
   for (int m = 0; m < kPrepMaxD / 32; ++m) {
     const int i = lane + 32 * m;
     kv[m] = i < d ? k[i] : 0.f;
+    av[m] = i < d ? a[i] : 0.f;
+    zv[m] = i < d ? zrow[i] : 0.f;
     ss += kv[m] * kv[m];
   }
   ss = warp_sum(ss);
@@ -496,16 +495,24 @@ general_delta_prepare_kernel(const float* __restrict__ proj, int ldp, float* __r
     if (i >= d) continue;
     const int c = h * d + i;
     const float u = kv[m] * inv;
-    const float rate = 1.0f / (1.0f + expf(-(a[i] + a_bias[c])));
-    float z = 0.f;
-    const float* w2row = w2 + (size_t)c * R;
-    for (int j = 0; j < R; ++j) z = fmaf(w2row[j], th[j], z);
-    z += w0[c];
-    const float decay = expf(-decay_scale / (1.0f + expf(-z)));
+    const float rate = 1.0f / (1.0f + expf(-(av[m] + a_bias[c])));
+    const float decay = expf(-decay_scale / (1.0f + expf(-(zv[m] + w0[c]))));
     out[c] = u;
     out[(size_t)H * d + c] = rate * u;
     out[(size_t)2 * H * d + c] = decay;
   }
+}
+
+// out[t, j] = tanh(in[t, j]) for the R columns of a strided float32 matrix, into the compute
+// type: the input of the decay's second (expanding) product.
+template <typename TO>
+__global__ void tanh_cols_kernel(const float* __restrict__ in, int ld, TO* __restrict__ out,
+                                 int R, long long total) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / R;
+  const int j = (int)(idx - t * R);
+  out[idx] = from_float<TO>(tanhf(in[(size_t)t * ld + j]));
 }
 
 template <int DREG, int MAXT>
@@ -668,16 +675,32 @@ static int launch_general(const float* proj, int ldp, const float* prep, int ldq
 }  // namespace cretif
 
 extern "C" int cretif_general_delta_prepare(const float* proj, int ldp, float* prep, int ldo,
-                                            const float* a_bias, const float* w2, const float* w0,
-                                            int R, int H, int d, int e, float unit_eps,
+                                            const float* a_bias, const float* z, int ldz,
+                                            const float* w0, int H, int d, int e, float unit_eps,
                                             float decay_scale, int T, void* stream) {
   if (T <= 0) return kOk;
-  if (H <= 0 || d <= 0 || e <= 0 || R <= 0 || R > 8192 || d > kPrepMaxD) return kBadArgument;
-  if (ldp < 3 * H * d + 2 * H * e + R || ldo < 3 * H * d) return kBadArgument;
+  if (H <= 0 || d <= 0 || e <= 0 || d > kPrepMaxD) return kBadArgument;
+  if (ldp < 3 * H * d + 2 * H * e || ldo < 3 * H * d || ldz < H * d) return kBadArgument;
   dim3 grid(T, (H + kPrepWarps - 1) / kPrepWarps);
   if (grid.y > 65535) return kBadArgument;
-  general_delta_prepare_kernel<<<grid, kPrepWarps * 32, sizeof(float) * R, (cudaStream_t)stream>>>(
-      proj, ldp, prep, ldo, a_bias, w2, w0, R, H, d, e, unit_eps, decay_scale);
+  general_delta_prepare_kernel<<<grid, kPrepWarps * 32, 0, (cudaStream_t)stream>>>(
+      proj, ldp, prep, ldo, a_bias, z, ldz, w0, H, d, e, unit_eps, decay_scale);
+  return launch_status();
+}
+
+extern "C" int cretif_tanh_cols(const float* in, int ld, void* out, int out_dt, int R, int T,
+                                void* stream) {
+  if (T <= 0 || R <= 0) return kOk;
+  if (ld < R) return kBadArgument;
+  const long long total = (long long)T * R;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (out_dt == kF32)
+    tanh_cols_kernel<float><<<blocks, 256, 0, st>>>(in, ld, (float*)out, R, total);
+  else if (out_dt == kBF16)
+    tanh_cols_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(in, ld, (__nv_bfloat16*)out, R, total);
+  else
+    return kBadDType;
   return launch_status();
 }
 

@@ -3,7 +3,7 @@
 // A step's (token, choice) pairs are sorted by expert, and each expert's rows are then one
 // slice of two grouped matrix products (gate|up with the activation in the epilogue, down):
 //
-// * moe_route (a warp per token): router logits z = W_r x in 32-bit (W_r float32; x as stored),
+// * moe_route (a CTA per token): router logits z = W_r x in 32-bit (W_r float32; x as stored),
 //   score s = 1 / (1 + e^-z), the `top` largest (ties: the lower index), weights = the scores
 //   as they are, or divided by their sum when asked.
 // * moe_group (one CTA): counts per expert, offsets, each pair's place in the sorted list and
@@ -30,28 +30,54 @@ namespace {
 constexpr int kTile = 64;
 constexpr int kMaxExpertsPerLane = 8;            // E <= 256
 
+// A CTA per token: its sixteen warps take the experts in turn (a dot product each, every load of
+// a row in flight at once where the width is a multiple of four), leave the logits in shared
+// memory, and warp 0 picks the `top` largest.
+constexpr int kRouteWarps = 16;
+constexpr int kMaxExperts = 32 * kMaxExpertsPerLane;
+
+__device__ __forceinline__ float4 ld4_as_float(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+__device__ __forceinline__ float4 ld4_as_float(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                     __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+}
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ wr, int E, int H,
-                 int top, int renorm, int* __restrict__ ids, float* __restrict__ wts, int T_tokens) {
+                 int top, int renorm, int* __restrict__ ids, float* __restrict__ wts, int vec) {
+  __shared__ float logits[kMaxExperts];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 8 + warp;
-  if (t >= T_tokens) return;
+  const int t = blockIdx.x;
   const T* row = x + (size_t)t * ldx;
-  float z[kMaxExpertsPerLane];
-#pragma unroll
-  for (int m = 0; m < kMaxExpertsPerLane; ++m) z[m] = -INFINITY;
-  for (int e = 0; e < E; ++e) {
+  for (int e = warp; e < E; e += kRouteWarps) {
     const float* w = wr + (size_t)e * H;
     float acc = 0.f;
-#pragma unroll 4
-    for (int i = lane; i < H; i += 32) acc = fmaf(w[i], to_float(row[i]), acc);
-    acc = warp_sum(acc);
-    if ((e & 31) == lane) {
-#pragma unroll
-      for (int m = 0; m < kMaxExpertsPerLane; ++m)
-        if (m == (e >> 5)) z[m] = acc;
+    if (vec) {
+      const int n4 = H >> 2;
+#pragma unroll 8
+      for (int i = lane; i < n4; i += 32) {
+        const float4 a = ld4_as_float(w + 4 * i), b = ld4_as_float(row + 4 * i);
+        acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc);
+        acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+      }
+    } else {
+#pragma unroll 8
+      for (int i = lane; i < H; i += 32) acc = fmaf(w[i], to_float(row[i]), acc);
     }
+    acc = warp_sum(acc);
+    if (lane == 0) logits[e] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float z[kMaxExpertsPerLane];
+#pragma unroll
+  for (int m = 0; m < kMaxExpertsPerLane; ++m) {
+    const int e = lane + 32 * m;
+    z[m] = e < E ? logits[e] : -INFINITY;
   }
   float total = 0.f;
   float my_w = 0.f;
@@ -341,6 +367,66 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int lda,
   }
 }
 
+// The same two products for a handful of pairs (a decode step), unsorted: a CTA owns 16 output
+// columns of ONE pair, streams its expert's rows for them once (16-byte loads, all of a row's in
+// flight together) against the pair's input row held in shared memory; warp w takes columns
+// 2w and 2w + 1.  mode 0: C[p, n] = silu(s g) (s u) from the gate row n and the up row N + n;
+// mode 1: C[p, n] = the product (times s with scale_at 2), float32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gemv_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, void* Cv, int ldc, int N,
+                int K, int top, int mode, int scale_at, const int* __restrict__ ids,
+                const float* __restrict__ wts, int vec) {
+  extern __shared__ __align__(16) unsigned char gemv_smem[];
+  T* xs = reinterpret_cast<T*>(gemv_smem);
+  const int p = blockIdx.y;
+  const int e = ids[p];
+  const float s = scale_at ? wts[p] : 1.f;
+  const T* arow = A + (size_t)(mode == 0 ? p / top : p) * lda;
+  if (vec) {
+    const int bytes = K * (int)sizeof(T);               // a multiple of 16
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(arow);
+    for (int o = threadIdx.x * 16; o < bytes; o += 256 * 16)
+      *reinterpret_cast<uint4*>(gemv_smem + o) = *reinterpret_cast<const uint4*>(src + o);
+  } else {
+    for (int i = threadIdx.x; i < K; i += 256) xs[i] = arow[i];
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t w_rows = (size_t)(mode == 0 ? 2 * N : N);
+  const T* We = W + (size_t)e * w_rows * K;
+  auto dot = [&](const T* wrow) {
+    float acc = 0.f;
+    if (vec) {
+#pragma unroll 4
+      for (int i = lane * 8; i < K; i += 256) {
+        float a[8], b[8];
+        load8(wrow + i, a);
+        load8(xs + i, b);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc = fmaf(a[q], b[q], acc);
+      }
+    } else {
+      for (int i = lane; i < K; i += 32) acc = fmaf(to_float(wrow[i]), to_float(xs[i]), acc);
+    }
+    return warp_sum(acc);
+  };
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int n = blockIdx.x * 16 + warp * 2 + c;
+    if (n >= N) continue;
+    if (mode == 0) {
+      const float sg = scale_at == 1 ? s : 1.f;
+      const float g = dot(We + (size_t)n * K) * sg, u = dot(We + ((size_t)N + n) * K) * sg;
+      if (lane == 0)
+        reinterpret_cast<T*>(Cv)[(size_t)p * ldc + n] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    } else {
+      const float v = dot(We + (size_t)n * K) * (scale_at == 2 ? s : 1.f);
+      if (lane == 0) reinterpret_cast<float*>(Cv)[(size_t)p * ldc + n] = v;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ rows, int ld, const int* __restrict__ place, int top,
                    float* __restrict__ y, int T, int H) {
@@ -348,7 +434,10 @@ moe_combine_kernel(const float* __restrict__ rows, int ld, const int* __restrict
   if (idx >= (long long)T * H) return;
   const int t = (int)(idx / H), c = (int)(idx - (long long)t * H);
   float acc = 0.f;
-  for (int k = 0; k < top; ++k) acc += rows[(size_t)place[(size_t)t * top + k] * ld + c];
+  for (int k = 0; k < top; ++k) {
+    const size_t pair = (size_t)t * top + k;
+    acc += rows[(place ? (size_t)place[pair] : pair) * ld + c];
+  }
   y[idx] = acc;
 }
 
@@ -364,13 +453,13 @@ extern "C" int cretif_moe_route(const void* x, int x_dt, int ldx, const float* r
   if (E <= 0 || E > 32 * kMaxExpertsPerLane || H <= 0 || top <= 0 || top > E || ldx < H)
     return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
-  const unsigned blocks = (unsigned)((T + 7) / 8);
+  const int vec = H % 4 == 0 && ldx % 4 == 0 && (((uintptr_t)x | (uintptr_t)router_w) & 15) == 0;
   if (x_dt == kF32)
-    moe_route_kernel<float><<<blocks, 256, 0, st>>>((const float*)x, ldx, router_w, E, H, top,
-                                                    renorm, ids, wts, T);
+    moe_route_kernel<float><<<T, kRouteWarps * 32, 0, st>>>((const float*)x, ldx, router_w, E, H,
+                                                            top, renorm, ids, wts, vec);
   else if (x_dt == kBF16)
-    moe_route_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, router_w,
-                                                            E, H, top, renorm, ids, wts, T);
+    moe_route_kernel<__nv_bfloat16><<<T, kRouteWarps * 32, 0, st>>>(
+        (const __nv_bfloat16*)x, ldx, router_w, E, H, top, renorm, ids, wts, vec);
   else
     return kBadDType;
   return launch_status();
@@ -430,6 +519,44 @@ extern "C" int cretif_moe_gemm(const void* A, int a_dt, int lda, const void* W, 
         offsets, tile_expert, tile_row0);
   else
     return kBadDType;
+  return launch_status();
+}
+
+// The products for few pairs, in the pairs' own order (no sorting): A, W, C as in cretif_moe_gemm
+// with C's rows indexed by the pair.
+extern "C" int cretif_moe_gemv(const void* A, int a_dt, int lda, const void* W, int w_dt, void* C,
+                               int ldc, int N, int K, int top, int mode, int scale_at,
+                               const int* ids, const float* wts, int P, void* stream) {
+  if (P <= 0) return kOk;
+  if (N <= 0 || K <= 0 || lda < K || ldc < N || top <= 0 || mode < 0 || mode > 1 ||
+      scale_at < 0 || scale_at > 2 || P > 65535 || a_dt != w_dt)
+    return kBadArgument;
+  const size_t esz = a_dt == kF32 ? 4 : 2;
+  const size_t smem = (size_t)K * esz;
+  if (smem > 96 * 1024) return kBadArgument;
+  const int vec = K % 8 == 0 && lda % 8 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0;
+  dim3 grid((N + 15) / 16, P);
+  cudaStream_t st = (cudaStream_t)stream;
+  typedef __nv_bfloat16 bf16;
+  if (a_dt == kF32) {
+    if (smem > 48 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(moe_gemv_kernel<float>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      if (err != cudaSuccess) return (int)err;
+    }
+    moe_gemv_kernel<float><<<grid, 256, smem, st>>>((const float*)A, lda, (const float*)W, C, ldc,
+                                                    N, K, top, mode, scale_at, ids, wts, vec);
+  } else if (a_dt == kBF16) {
+    if (smem > 48 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(moe_gemv_kernel<bf16>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      if (err != cudaSuccess) return (int)err;
+    }
+    moe_gemv_kernel<bf16><<<grid, 256, smem, st>>>((const bf16*)A, lda, (const bf16*)W, C, ldc, N,
+                                                   K, top, mode, scale_at, ids, wts, vec);
+  } else {
+    return kBadDType;
+  }
   return launch_status();
 }
 

@@ -444,22 +444,31 @@ def conv_headnorm_kv_append(proj, conv_w, conv_state, tok_pos, tok_seq, seq_slot
 
 
 # ------------------------------------------------------------------ generalized delta rule
-def general_delta_prepare(proj, prep, a_bias, w2, w0, H: int, d: int, e: int, unit_eps: float,
+def tanh_cols(rows, out) -> None:
+    """out = tanh(rows) for a strided float32 [T, R] view, in out's element type."""
+    _need(rows, "rows", torch.float32, 2); _need(out, "out", dim=2)
+    if out.shape != rows.shape or not out.is_contiguous():
+        raise KernelError("tanh_cols: out must be a contiguous tensor of rows' shape")
+    _check(lib().cretif_tanh_cols(_p(rows), _rows(rows, "rows"), _p(out), _dt(out), rows.shape[1],
+                                  rows.shape[0], _stream()), "tanh_cols")
+
+
+def general_delta_prepare(proj, prep, a_bias, z, w0, H: int, d: int, e: int, unit_eps: float,
                           decay_scale: float) -> None:
-    """``proj`` float32 [T, 3Hd + 2He + R] = [r | k | v | gate | a | w1]; ``prep`` [T, 3Hd] =
-    [unit key | removal along it | decay], see delta_rule.cu."""
+    """``proj`` float32 [T, 3Hd + 2He + ...] = [r | k | v | gate | a | ...]; ``z`` [T, Hd] the
+    decay's expanded low-rank product; ``prep`` [T, 3Hd] = [unit key | removal along it |
+    decay], see delta_rule.cu."""
     _need(proj, "proj", torch.float32, 2); _need(prep, "prep", torch.float32, 2)
-    _need(w2, "w2", torch.float32, 2); _need(w0, "w0", torch.float32, 1)
+    _need(z, "z", torch.float32, 2); _need(w0, "w0", torch.float32, 1)
     _need(a_bias, "a_bias", torch.float32, 1)
-    R = w2.shape[1]
-    if (w2.shape[0] != H * d or not w2.is_contiguous() or w0.numel() != H * d
-            or a_bias.numel() != H * d or proj.shape[1] < 3 * H * d + 2 * H * e + R
+    if (z.shape[1] < H * d or z.shape[0] != proj.shape[0] or w0.numel() != H * d
+            or a_bias.numel() != H * d or proj.shape[1] < 3 * H * d + 2 * H * e
             or prep.shape[1] < 3 * H * d or prep.shape[0] != proj.shape[0]):
         raise KernelError("general_delta_prepare: sizes do not fit")
     _check(lib().cretif_general_delta_prepare(
-        _p(proj), _rows(proj, "proj"), _p(prep), _rows(prep, "prep"), _p(a_bias), _p(w2), _p(w0),
-        R, H, d, e, ctypes.c_float(unit_eps), ctypes.c_float(decay_scale), proj.shape[0],
-        _stream()), "general_delta_prepare")
+        _p(proj), _rows(proj, "proj"), _p(prep), _rows(prep, "prep"), _p(a_bias), _p(z),
+        _rows(z, "z"), _p(w0), H, d, e, ctypes.c_float(unit_eps), ctypes.c_float(decay_scale),
+        proj.shape[0], _stream()), "general_delta_prepare")
 
 
 def general_delta_recurrence(proj, prep, gate, state, cu_seqlens, seq_slot, B: int, H: int, d: int,
@@ -550,12 +559,30 @@ def moe_gemm(a, w, c, top: int, mode: int, scale_at: int, wts, order, offsets, t
         tile_expert.numel(), use_mma, _stream()), "moe_gemm")
 
 
+def moe_gemv(a, w, c, top: int, mode: int, scale_at: int, ids, wts) -> None:
+    """``moe_gemm`` for a handful of pairs, in the pairs' own order (nothing is sorted): a CTA
+    per pair and 16 output columns streams the expert's rows once."""
+    _need(a, "a", dim=2); _need(w, "w", a.dtype, 3); _need(c, "c", dim=2)
+    _need(ids, "ids", torch.int32); _need(wts, "wts", torch.float32)
+    K, N, P = a.shape[1], c.shape[1], ids.numel()
+    if (w.shape[2] != K or w.shape[1] != (2 * N if mode == 0 else N) or not w.is_contiguous()
+            or c.dtype != (a.dtype if mode == 0 else torch.float32) or c.shape[0] != P
+            or wts.numel() != P or not ids.is_contiguous() or not wts.is_contiguous()):
+        raise KernelError("moe_gemv: sizes or element types do not fit")
+    _check(lib().cretif_moe_gemv(
+        _p(a), _dt(a), _rows(a, "a"), _p(w), _dt(w), _p(c), _rows(c, "c"), N, K, top, mode,
+        scale_at, _p(ids), _p(wts), P, _stream()), "moe_gemv")
+
+
 def moe_combine(rows, place, top: int, y) -> None:
-    """y[t] = the sum of the token's ``top`` rows of ``rows`` (float32), in their order."""
+    """y[t] = the sum of the token's ``top`` rows of ``rows`` (float32), in their order;
+    ``place`` None: the rows are in the pairs' own order."""
     _need(rows, "rows", torch.float32, 2); _need(y, "y", torch.float32, 2)
-    _need(place, "place", torch.int32)
+    if place is not None:
+        _need(place, "place", torch.int32)
     T, H = y.shape
-    if rows.shape[1] != H or place.numel() != T * top or not y.is_contiguous():
+    if (rows.shape[1] != H or (place is not None and place.numel() != T * top)
+            or rows.shape[0] < T * top or not y.is_contiguous()):
         raise KernelError("moe_combine: sizes do not fit")
     _check(lib().cretif_moe_combine(_p(rows), _rows(rows, "rows"), _p(place), top, _p(y), T, H,
                                     _stream()), "moe_combine")

@@ -175,7 +175,7 @@ class GeneralDeltaRule(Part):
         self.w_in = self._matrix(torch.cat([t["r"], t["k"], t["v"], t["gate"], t["a"], t["w1"]],
                                            dim=0))
         self.a_bias = self._vector32(t["a_bias"])
-        self.w2 = self._vector32(t["w2"])
+        self.w2 = self._matrix(t["w2"])                  # the expanding product's matrix
         self.w0 = self._vector32(t["w0"])
         self.norm_w = self._vector32(t["norm"])
         self.w_o = self._matrix(t["o"])
@@ -188,7 +188,11 @@ class GeneralDeltaRule(Part):
         T = ctx.T
         proj = linear(x, self.w_in, out_dtype=torch.float32)     # [T, 3Hd + 2He + rank]
         prep = torch.empty((T, 3 * H * d), dtype=torch.float32, device=x.device)
-        ops.general_delta_prepare(proj, prep, self.a_bias, self.w2, self.w0, H, d, e,
+        # the decay's low rank: tanh of the narrow projection, expanded by a product of its own
+        low = torch.empty((T, self.rank), dtype=self.dtype, device=x.device)
+        ops.tanh_cols(proj[:, 3 * H * d + 2 * H * e:], low)
+        z = linear(low, self.w2, out_dtype=torch.float32)
+        ops.general_delta_prepare(proj, prep, self.a_bias, z, self.w0, H, d, e,
                                   self.unit_eps, self.decay_scale)
         out = torch.empty((T, H * e), dtype=self.dtype, device=x.device)
         gate = proj[:, 2 * H * d + H * e:2 * H * d + 2 * H * e]
@@ -199,4 +203,5 @@ class GeneralDeltaRule(Part):
 
     def weight_bytes(self):
         return ((self.w_in.numel() + self.w_o.numel()) * self.w_o.element_size()
-                + 4 * (self.w2.numel() + 3 * self.nh * self.hd + self.nh * self.vd))
+                + self.w2.numel() * self.w2.element_size()
+                + 4 * (3 * self.nh * self.hd + self.nh * self.vd))

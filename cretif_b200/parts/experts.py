@@ -22,6 +22,21 @@ from ..weights.loader import WeightSpec
 from .base import Part, register_part
 
 
+# Steps of at most this many (token, choice) pairs take the streaming kernel, which reads an
+# expert's matrices once per pair; beyond it the pairs are sorted and an expert's rows share a
+# tile's read.
+FEW_PAIRS = 32
+_few_pairs_off = False
+
+
+def few_pairs_off(on=None) -> bool:
+    """Switch the few-pairs kernel off (tests run both ways on one step); returns the state."""
+    global _few_pairs_off
+    if on is not None:
+        _few_pairs_off = bool(on)
+    return _few_pairs_off
+
+
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(Part):
     """params: ``num_experts``, ``top``, ``intermediate_size`` (of one expert), ``weight_on``
@@ -71,6 +86,16 @@ class RoutedExperts(Part):
         ids = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         wts = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         ops.moe_route(x, self.router, self.top, ids, wts, renorm=self.renorm)
+        on_input = self.weight_on == "input"
+        act = torch.empty((P, self.inter), dtype=self.dtype, device=dev)
+        rows = torch.empty((P, H), dtype=torch.float32, device=dev)
+        y = torch.empty((T, H), dtype=torch.float32, device=dev)
+        if P <= FEW_PAIRS and not few_pairs_off():
+            # a handful of pairs: every pair streams its expert's rows, nothing is sorted
+            ops.moe_gemv(x, self.w_gu, act, self.top, 0, 1 if on_input else 0, ids, wts)
+            ops.moe_gemv(act, self.w_down, rows, self.top, 1, 0 if on_input else 2, ids, wts)
+            ops.moe_combine(rows, None, self.top, y)
+            return y
         tiles = ops.moe_max_tiles(P, self.E)
         idx = torch.empty(self.E + 1 + 2 * P + 2 * tiles, dtype=torch.int32, device=dev)
         offsets, place, order = idx[:self.E + 1], idx[self.E + 1:self.E + 1 + P], \
@@ -78,14 +103,10 @@ class RoutedExperts(Part):
         tile_expert, tile_row0 = idx[self.E + 1 + 2 * P:self.E + 1 + 2 * P + tiles], \
             idx[self.E + 1 + 2 * P + tiles:]
         ops.moe_group(ids, self.E, offsets, place, order, tile_expert, tile_row0)
-        act = torch.empty((P, self.inter), dtype=self.dtype, device=dev)
-        on_input = self.weight_on == "input"
         ops.moe_gemm(x, self.w_gu, act, self.top, 0, 1 if on_input else 0, wts, order, offsets,
                      tile_expert, tile_row0)
-        rows = torch.empty((P, H), dtype=torch.float32, device=dev)
         ops.moe_gemm(act, self.w_down, rows, self.top, 1, 0 if on_input else 2, wts, order,
                      offsets, tile_expert, tile_row0)
-        y = torch.empty((T, H), dtype=torch.float32, device=dev)
         ops.moe_combine(rows, place, self.top, y)
         return y
 

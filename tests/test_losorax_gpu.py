@@ -388,8 +388,11 @@ def test_general_delta_rule_kernels_in_pieces(H, d, e, R):
         rows = proj[at:at + n].cuda().contiguous()
         prep = torch.empty(n, 3 * H * d, device="cuda")
         cu = torch.tensor([0, n], dtype=torch.int32, device="cuda")
-        ops.general_delta_prepare(rows, prep, a_bias.cuda(), w2.cuda(), w0.cuda(), H, d, e, 1e-6,
-                                  scale)
+        low = torch.empty(n, R, device="cuda")
+        ops.tanh_cols(rows[:, o_w:], low)
+        z = torch.empty(n, H * d, device="cuda")
+        ops.gemm_simt(low, w2.cuda(), z)
+        ops.general_delta_prepare(rows, prep, a_bias.cuda(), z, w0.cuda(), H, d, e, 1e-6, scale)
         out = torch.empty(n, H * e, device="cuda")
         ops.general_delta_recurrence(rows, prep, rows[:, o_g:o_a], state, cu, seq_slot, 1, H, d, e,
                                      norm_w.cuda(), 1e-5, out)
@@ -402,6 +405,7 @@ def test_general_delta_rule_kernels_in_pieces(H, d, e, R):
 
 
 @pytest.mark.parametrize("T,H,F,E,top", [(1, 64, 32, 6, 2), (70, 96, 40, 5, 3), (9, 48, 48, 1, 1),
+                                         (8, 100, 36, 9, 4), (3, 70, 30, 4, 2),
                                          (300, 40, 24, 7, 2), (130, 64, 100, 12, 1),
                                          (33, 72, 20, 40, 4)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -424,15 +428,21 @@ def test_routed_experts_kernels(T, H, F, E, top, dtype):
     x = torch.randn(T, H, generator=g).to(dtype)
     want = plain.routed_experts(x.double(), W, "m.", {"router": {"experts": E, "top": top}})
     tol = 1e-5 if dtype == torch.float32 else 3e-2
-    for simt in ((True,) if dtype == torch.float32 else (True, False)):
+    from cretif_b200.parts import experts
+    ways = [(True, True)] + ([(False, True)] if dtype == torch.bfloat16 else [])
+    if T * top <= experts.FEW_PAIRS:
+        ways.append((True, False))                     # the few-pairs kernel
+    for simt, sorted_tiles in ways:
         ops.moe_simt_only(simt)
+        experts.few_pairs_off(sorted_tiles)
         try:
             got = part.forward(x.cuda(), None)
         finally:
             ops.moe_simt_only(False)
+            experts.few_pairs_off(False)
         err = (got.cpu().double() - want).abs().max(dim=1).values / want.abs().max()
         # (in bfloat16 the activation between the products is rounded)
-        assert err.max() <= tol, (simt, float(err.max()))
+        assert err.max() <= tol, (simt, sorted_tiles, float(err.max()))
     # the weight on the output instead is another function
     part_out = RoutedExperts({**params, "weight_on": "output"}, H, dtype, "cuda")
     part_out.load(tensors)
