@@ -128,9 +128,13 @@ int cretif_moe_gemm(const void* A, int a_dt, int lda, const void* W, int w_dt, v
 int cretif_moe_gemv(const void* A, int a_dt, int lda, const void* W, int w_dt, void* C, int ldc,
                     int N, int K, int top, int mode, int scale_at, const int* ids,
                     const float* wts, int P, void* stream);
-// place may be null: the rows are in the pairs' own order.
-int cretif_moe_combine(const float* rows, int ld, const int* place, int top, float* y, int T,
-                       int H, void* stream);
+int cretif_moe_group_padded(const int* ids, int P, int E, int tile, int* place, int* tile_expert,
+                            int max_tiles, int* used, void* stream);
+int cretif_moe_gather_rows(const void* x, int ldx, void* xs, int lds, const int* place,
+                           const float* wts, int top, int K, int P, void* stream);
+// place may be null: the rows are in the pairs' own order; wts may be null: no weights.
+int cretif_moe_combine(const float* rows, int ld, const int* place, int top, const float* wts,
+                       float* y, int T, int H, void* stream);
 
 // After a decode step: ids <- sampled (if given), positions and lengths + 1.
 int cretif_advance_decode(int* tok_ids, int* tok_pos, int* seq_start, const int* sampled, int B,
@@ -182,6 +186,15 @@ int cretif_set_tc_pair(int mode);
 // the stacked q|k|v matrix (head_dim 64 or 128, rotary over the whole head).
 int cretif_gemm_tc_silu(const void* A, const void* Wgu, void* act, int M, int I, int K, int lda,
                         int ldw, unsigned int* fault, void* stream);
+// The same products in groups: A [M, K], M a multiple of 128, whose 128-row tiles each belong to a
+// group (tile_group[M / 128]; *used_m_tiles tiles are in use, the others are left alone), and
+// W [groups, N, K] ([groups, 2 I, K] interleaved as above); C float32 [M, N], act [M, I].
+int cretif_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K, int lda,
+                           int ldw, int ldc, int groups, const int* tile_group,
+                           const int* used_m_tiles, unsigned int* fault, void* stream);
+int cretif_gemm_tc_silu_grouped(const void* A, const void* Wgu, void* act, int M, int I, int K,
+                                int lda, int ldw, int groups, const int* tile_group,
+                                const int* used_m_tiles, unsigned int* fault, void* stream);
 int cretif_gemm_tc_qkv_rope(const void* A, const void* Wqkv, void* Q, int ldq, const float* cos_t,
                             const float* sin_t, int pairing, int nh, int nkv, int hd,
                             const int* tok_pos, const int* tok_seq, const int* seq_slot,

@@ -89,6 +89,11 @@ struct TcEpi {
   int table_stride;
   __nv_bfloat16* kc; __nv_bfloat16* vc;
   int bt, write_cache;
+  // Grouped product (all null/0 for an ordinary one): the rows of A come in groups of whole
+  // 128-row tiles and group g multiplies by rows [g * group_rows, (g + 1) * group_rows) of W.
+  // tile_group[mt] is the group of row tile mt, *used_m_tiles how many row tiles are in use
+  // (the rest of the grid's tiles is left alone); both are written by the kernel before.
+  const int* tile_group; int group_rows; const int* used_m_tiles;
 };
 
 __device__ __forceinline__ float round_bf16(float x) {
@@ -143,7 +148,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     t.nt += step_n;
     if (t.nt >= n_n_tiles) { t.nt -= n_n_tiles; ++t.mt; }
   };
-  const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  // A grouped product learns its tiles from the kernel before it: wait for that one first.
+  const bool grouped = ep.tile_group != nullptr;
+  int tiles_now = n_tiles;
+  if (grouped) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (ep.used_m_tiles) tiles_now = min(n_tiles, max(*ep.used_m_tiles, 0) * n_n_tiles);
+  }
+  const int my_tiles = (int)blockIdx.x < tiles_now ? (tiles_now - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  auto w_row = [&](const Tile& t) {          // first row of W that tile t multiplies by
+    return t.nt * BN + (grouped ? max(ep.tile_group[t.mt], 0) * ep.group_rows : 0);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kTcStages; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], 1); }
@@ -173,7 +188,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int early = num_kb < kTcStages ? num_kb : kTcStages;
       for (int kb = 0; kb < early; ++kb) {
         tc::mbar_expect_tx(&full[kb], (uint32_t)L::kStage);
-        tc::tma_load_2d(smem + kb * L::kStage + L::kATile, &map_w, kb * kTcBK, t.nt * BN, &full[kb]);
+        tc::tma_load_2d(smem + kb * L::kStage + L::kATile, &map_w, kb * kTcBK, w_row(t), &full[kb]);
       }
       asm volatile("griddepcontrol.wait;" ::: "memory");
       stamp(2);
@@ -192,7 +207,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           unsigned char* stage = smem + s * L::kStage;
           tc::mbar_expect_tx(&full[s], (uint32_t)L::kStage);
           tc::tma_load_2d(stage, &map_a, kb * kTcBK, t.mt * kTcBM, &full[s]);
-          tc::tma_load_2d(stage + L::kATile, &map_w, kb * kTcBK, t.nt * BN, &full[s]);
+          tc::tma_load_2d(stage + L::kATile, &map_w, kb * kTcBK, w_row(t), &full[s]);
           if (++s == kTcStages) { s = 0; ++turn; }
         }
       }
@@ -971,11 +986,12 @@ static cudaError_t launch_tc_kernel(const cudaLaunchConfig_t& cfg, int smem,
 
 template <int BN, int EPI, typename TC>
 static int launch_tc(const void* A, const void* W, const TcEpi& ep_in, int M, int N, int K, int lda,
-                     int ldw, unsigned int* fault, cudaStream_t st) {
+                     int ldw, unsigned int* fault, cudaStream_t st, int w_rows = 0) {
+  // w_rows: rows of W when it holds more than the N of one product (a grouped product's groups)
   TcEpi ep = ep_in;
   CUtensorMap map_a, map_w, map_c = {};
   if (make_tile_map_bf16(&map_a, A, M, K, lda, kTcBM)) return kBadArgument;
-  if (make_tile_map_bf16(&map_w, W, N, K, ldw, BN)) return kBadArgument;
+  if (make_tile_map_bf16(&map_w, W, w_rows ? w_rows : N, K, ldw, BN)) return kBadArgument;
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;
@@ -1151,6 +1167,51 @@ extern "C" int cretif_gemm_tc_silu(const void* A, const void* Wgu, void* act, in
                                                   (cudaStream_t)stream);
   return launch_tc<128, kTcSilu, __nv_bfloat16>(A, Wgu, ep, M, 2 * I, K, lda, ldw, fault,
                                                 (cudaStream_t)stream);
+}
+
+// Grouped products: A [M, K] with M a multiple of 128 whose row tiles belong to groups
+// (tile_group[M / 128], -1 beyond the tiles in use; *used_m_tiles of them are), W [groups, N, K].
+// C [M, N] float32 = A W[g]^T ...
+extern "C" int cretif_gemm_tc_grouped(const void* A, const void* W, void* C, int M, int N, int K,
+                                      int lda, int ldw, int ldc, int groups, const int* tile_group,
+                                      const int* used_m_tiles, unsigned int* fault, void* stream) {
+  if (M <= 0 || N <= 0 || groups <= 0) return kOk;
+  if (!tc_operands_ok(A, W, M, K, lda, ldw) || M % kTcBM || ldc < N || ldc % 4 || !tile_group ||
+      (long long)groups * N > 0x7fffffffLL)
+    return kBadArgument;
+  if (((uintptr_t)C) & 15) return kMisaligned;
+  TcEpi ep = {};
+  ep.C = C; ep.ldc = ldc; ep.accumulate = 0;
+  ep.tile_group = tile_group; ep.group_rows = N; ep.used_m_tiles = used_m_tiles;
+  const long long mt = M / kTcBM;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (mt * ((N + 255) / 256) >= 148)
+    return launch_tc<256, kTcStore, float>(A, W, ep, M, N, K, lda, ldw, fault, st, groups * N);
+  if (mt * ((N + 127) / 128) >= 148)
+    return launch_tc<128, kTcStore, float>(A, W, ep, M, N, K, lda, ldw, fault, st, groups * N);
+  return launch_tc<64, kTcStore, float>(A, W, ep, M, N, K, lda, ldw, fault, st, groups * N);
+}
+
+// ... and act [M, I] = silu(A Wg[g]^T) * (A Wu[g]^T), Wgu [groups, 2 I, K] with gate and up rows
+// interleaved in blocks of 64 inside each group.
+extern "C" int cretif_gemm_tc_silu_grouped(const void* A, const void* Wgu, void* act, int M, int I,
+                                           int K, int lda, int ldw, int groups,
+                                           const int* tile_group, const int* used_m_tiles,
+                                           unsigned int* fault, void* stream) {
+  if (M <= 0 || I <= 0 || groups <= 0) return kOk;
+  if (!tc_operands_ok(A, Wgu, M, K, lda, ldw) || I % 64 || M % kTcBM || !tile_group ||
+      (long long)groups * 2 * I > 0x7fffffffLL)
+    return kBadArgument;
+  if (((uintptr_t)act) & 15) return kMisaligned;
+  TcEpi ep = {};
+  ep.act = (__nv_bfloat16*)act; ep.I = I;
+  ep.tile_group = tile_group; ep.group_rows = 2 * I; ep.used_m_tiles = used_m_tiles;
+  const long long wide_tiles = (long long)((2 * I + 255) / 256) * (M / kTcBM);
+  if (wide_tiles >= 4 * 148)
+    return launch_tc<256, kTcSilu, __nv_bfloat16>(A, Wgu, ep, M, 2 * I, K, lda, ldw, fault,
+                                                  (cudaStream_t)stream, groups * 2 * I);
+  return launch_tc<128, kTcSilu, __nv_bfloat16>(A, Wgu, ep, M, 2 * I, K, lda, ldw, fault,
+                                                (cudaStream_t)stream, groups * 2 * I);
 }
 
 // q|k|v = A·Wqkv^T with rotary on q and k; q to Q, k and v into the block cache.

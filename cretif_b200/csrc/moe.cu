@@ -18,6 +18,13 @@
 //   32-bit FMA on the CUDA cores (any element type, the float32 path and the yardstick) and
 //   bfloat16 on the tensor cores (mma.sync through the warp-level matrix API).
 // * moe_combine: y[t] = sum over the token's choices, in the order of the choices (32-bit).
+// * Many pairs in bfloat16 go to the library's tcgen05 product in its grouped mode instead
+//   (gemm_tc.cu): moe_group pads every expert's rows to whole 128-row tiles, moe_gather_rows
+//   writes the A operand in that order -- the token's row times its router weight, which is
+//   where a weight on the expert's input belongs -- and the two products read which expert a row
+//   tile belongs to.
+// * A handful of pairs (a decode step) are not sorted at all: moe_gemv streams an expert's rows
+//   once per pair.
 #include <mma.h>
 
 #include "api.h"
@@ -117,10 +124,13 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ wr,
     for (int k = 32; k < top; ++k) wts[(size_t)t * top + k] /= total;
 }
 
+// tile: rows of a tile; padded: every expert's rows start at a multiple of `tile` (the sorted
+// list then has gaps, and a tile never holds rows of two experts).  used[0] = tiles in use.
 __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ offsets,
                  int* __restrict__ place, int* __restrict__ order, int* __restrict__ tile_expert,
-                 int* __restrict__ tile_row0, int max_tiles) {
+                 int* __restrict__ tile_row0, int max_tiles, int tile, int padded,
+                 int* __restrict__ used) {
   extern __shared__ int sh[];                    // counts [E], cursor [E], start [E + 1]
   int* counts = sh;
   int* cursor = sh + E;
@@ -130,26 +140,50 @@ moe_group_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ of
   for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&counts[ids[p]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
-    int at = 0, tile = 0;
+    int at = 0, n_tiles = 0;
     for (int e = 0; e < E; ++e) {
       start[e] = at;
-      offsets[e] = at;
-      for (int r = 0; r < counts[e] && tile < max_tiles; r += kTile, ++tile) {
-        tile_expert[tile] = e;
-        tile_row0[tile] = at + r;
+      if (offsets) offsets[e] = at;
+      for (int r = 0; r < counts[e] && n_tiles < max_tiles; r += tile, ++n_tiles) {
+        tile_expert[n_tiles] = e;
+        if (tile_row0) tile_row0[n_tiles] = at + r;
       }
-      at += counts[e];
+      at += padded ? (counts[e] + tile - 1) / tile * tile : counts[e];
     }
     start[E] = at;
-    offsets[E] = at;
-    for (; tile < max_tiles; ++tile) tile_expert[tile] = -1;
+    if (offsets) offsets[E] = at;
+    if (used) used[0] = n_tiles;
+    for (; n_tiles < max_tiles; ++n_tiles) tile_expert[n_tiles] = -1;
   }
   __syncthreads();
   for (int p = threadIdx.x; p < P; p += blockDim.x) {
     const int e = ids[p];
     const int at = start[e] + atomicAdd(&cursor[e], 1);
     place[p] = at;
-    order[at] = p;
+    if (order) order[at] = p;
+  }
+}
+
+// xs[place[p], :] = x[p / top, :] (times the pair's router weight, rounded once): the rows of a
+// grouped product's A operand, gathered into the padded sorted order.
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+                       __nv_bfloat16* __restrict__ xs, int lds, const int* __restrict__ place,
+                       const float* __restrict__ wts, int top, int K, int vec) {
+  const int p = blockIdx.x;
+  const __nv_bfloat16* src = x + (size_t)(p / top) * ldx;
+  __nv_bfloat16* dst = xs + (size_t)place[p] * lds;
+  const float s = wts ? wts[p] : 1.f;
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < K; i += 256 * 8) {
+      float v[8];
+      load8(src + i, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] *= s;
+      store8(dst + i, v);
+    }
+  } else {
+    for (int i = threadIdx.x; i < K; i += 256) dst[i] = __float2bfloat16_rn(to_float(src[i]) * s);
   }
 }
 
@@ -429,14 +463,15 @@ moe_gemv_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, void*
 
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ rows, int ld, const int* __restrict__ place, int top,
-                   float* __restrict__ y, int T, int H) {
+                   const float* __restrict__ wts, float* __restrict__ y, int T, int H) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)T * H) return;
   const int t = (int)(idx / H), c = (int)(idx - (long long)t * H);
   float acc = 0.f;
   for (int k = 0; k < top; ++k) {
     const size_t pair = (size_t)t * top + k;
-    acc += rows[(place ? (size_t)place[pair] : pair) * ld + c];
+    const float v = rows[(place ? (size_t)place[pair] : pair) * ld + c];
+    acc += wts ? wts[pair] * v : v;
   }
   y[idx] = acc;
 }
@@ -470,7 +505,31 @@ extern "C" int cretif_moe_group(const int* ids, int P, int E, int* offsets, int*
   if (P <= 0) return kOk;
   if (E <= 0 || E > 4096 || max_tiles < (P + kTile - 1) / kTile + E) return kBadArgument;
   moe_group_kernel<<<1, 1024, sizeof(int) * (3 * E + 1), (cudaStream_t)stream>>>(
-      ids, P, E, offsets, place, order, tile_expert, tile_row0, max_tiles);
+      ids, P, E, offsets, place, order, tile_expert, tile_row0, max_tiles, kTile, 0, nullptr);
+  return launch_status();
+}
+
+// The padded order for the tensor-core grouped products: every expert's rows start at a multiple
+// of `tile` rows; place [P], tile_expert [max_tiles >= ceil(P / tile) + E], used [1].
+extern "C" int cretif_moe_group_padded(const int* ids, int P, int E, int tile, int* place,
+                                       int* tile_expert, int max_tiles, int* used, void* stream) {
+  if (P <= 0) return kOk;
+  if (E <= 0 || E > 4096 || tile <= 0 || max_tiles < (P + tile - 1) / tile + E || !used)
+    return kBadArgument;
+  moe_group_kernel<<<1, 1024, sizeof(int) * (3 * E + 1), (cudaStream_t)stream>>>(
+      ids, P, E, nullptr, place, nullptr, tile_expert, nullptr, max_tiles, tile, 1, used);
+  return launch_status();
+}
+
+// xs[place[p]] = x[p / top] * wts[p] (wts may be null), bfloat16 rows of K columns.
+extern "C" int cretif_moe_gather_rows(const void* x, int ldx, void* xs, int lds, const int* place,
+                                      const float* wts, int top, int K, int P, void* stream) {
+  if (P <= 0) return kOk;
+  if (K <= 0 || ldx < K || lds < K || top <= 0) return kBadArgument;
+  const int vec = K % 8 == 0 && ldx % 8 == 0 && lds % 8 == 0 &&
+                  (((uintptr_t)x | (uintptr_t)xs) & 15) == 0;
+  moe_gather_rows_kernel<<<P, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)xs, lds, place, wts, top, K, vec);
   return launch_status();
 }
 
@@ -560,11 +619,11 @@ extern "C" int cretif_moe_gemv(const void* A, int a_dt, int lda, const void* W, 
   return launch_status();
 }
 
-extern "C" int cretif_moe_combine(const float* rows, int ld, const int* place, int top, float* y,
-                                  int T, int H, void* stream) {
+extern "C" int cretif_moe_combine(const float* rows, int ld, const int* place, int top,
+                                  const float* wts, float* y, int T, int H, void* stream) {
   if (T <= 0) return kOk;
   if (H <= 0 || ld < H || top <= 0) return kBadArgument;
   const unsigned blocks = (unsigned)(((long long)T * H + 255) / 256);
-  moe_combine_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(rows, ld, place, top, y, T, H);
+  moe_combine_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(rows, ld, place, top, wts, y, T, H);
   return launch_status();
 }

@@ -574,9 +574,83 @@ def moe_gemv(a, w, c, top: int, mode: int, scale_at: int, ids, wts) -> None:
         scale_at, _p(ids), _p(wts), P, _stream()), "moe_gemv")
 
 
-def moe_combine(rows, place, top: int, y) -> None:
-    """y[t] = the sum of the token's ``top`` rows of ``rows`` (float32), in their order;
-    ``place`` None: the rows are in the pairs' own order."""
+MOE_TC_TILE = 128
+
+
+def moe_tc_tiles(pairs: int, experts: int) -> int:
+    """Row tiles of the padded order: every expert may leave one tile partly empty."""
+    return -(-pairs // MOE_TC_TILE) + experts
+
+
+def moe_group_padded(ids, experts: int, place, tile_expert, used) -> None:
+    """The order for the tensor-core grouped products: every expert's rows start at a multiple
+    of 128; ``place`` [P] is a pair's row, ``tile_expert`` [tiles] a tile's expert (-1: unused),
+    ``used`` [1] the number of tiles in use."""
+    for name, t in (("ids", ids), ("place", place), ("tile_expert", tile_expert), ("used", used)):
+        _need(t, name, torch.int32)
+        if not t.is_contiguous():
+            raise KernelError(f"moe_group_padded: {name} must be contiguous")
+    P = ids.numel()
+    if place.numel() != P or tile_expert.numel() < moe_tc_tiles(P, experts) or used.numel() != 1:
+        raise KernelError("moe_group_padded: sizes do not fit")
+    _check(lib().cretif_moe_group_padded(_p(ids), P, experts, MOE_TC_TILE, _p(place),
+                                         _p(tile_expert), tile_expert.numel(), _p(used),
+                                         _stream()), "moe_group_padded")
+
+
+def moe_gather_rows(x, xs, place, wts, top: int) -> None:
+    """xs[place[p]] = x[p // top] * wts[p] (``wts`` None: as it is), bfloat16."""
+    _need(x, "x", torch.bfloat16, 2); _need(xs, "xs", torch.bfloat16, 2)
+    _need(place, "place", torch.int32)
+    if xs.shape[1] != x.shape[1] or place.numel() != x.shape[0] * top:
+        raise KernelError("moe_gather_rows: sizes do not fit")
+    _check(lib().cretif_moe_gather_rows(_p(x), _rows(x, "x"), _p(xs), _rows(xs, "xs"), _p(place),
+                                        _p(wts), top, x.shape[1], place.numel(), _stream()),
+           "moe_gather_rows")
+
+
+def moe_tc_supported(x, w_gu, w_down) -> bool:
+    """Whether the grouped tensor-core products take these operands (bfloat16, widths that are
+    multiples of 8, an expert width that is a multiple of 64)."""
+    K, F = x.shape[1], w_down.shape[2]
+    return (x.dtype == torch.bfloat16 and w_gu.dtype == torch.bfloat16 and K % 8 == 0
+            and F % 64 == 0 and not _moe_simt_only)
+
+
+def gemm_tc_silu_grouped(xs, w_gu, act, tile_expert, used) -> None:
+    """act = silu(xs Wg[e]ᵀ) ⊙ (xs Wu[e]ᵀ) tile by tile; ``w_gu`` [E, 2F, K] with gate and up
+    rows interleaved in blocks of 64 inside each expert."""
+    _need(xs, "xs", torch.bfloat16, 2); _need(w_gu, "w_gu", torch.bfloat16, 3)
+    _need(act, "act", torch.bfloat16, 2)
+    M, K = xs.shape
+    E, F = w_gu.shape[0], w_gu.shape[1] // 2
+    if (M % MOE_TC_TILE or tuple(act.shape) != (M, F) or w_gu.shape[2] != K
+            or not w_gu.is_contiguous() or not act.is_contiguous()
+            or tile_expert.numel() < M // MOE_TC_TILE):
+        raise KernelError("gemm_tc_silu_grouped: sizes do not fit")
+    _check(lib().cretif_gemm_tc_silu_grouped(
+        _p(xs), _p(w_gu), _p(act), M, F, K, _rows(xs, "xs"), K, E, _p(tile_expert), _p(used),
+        _p(fault_word(xs.device)), _stream()), "gemm_tc_silu_grouped")
+
+
+def gemm_tc_grouped(a, w, c, tile_expert, used) -> None:
+    """c (float32) = a W[e]ᵀ tile by tile; ``w`` [E, N, K]."""
+    _need(a, "a", torch.bfloat16, 2); _need(w, "w", torch.bfloat16, 3)
+    _need(c, "c", torch.float32, 2)
+    M, K = a.shape
+    E, N = w.shape[0], w.shape[1]
+    if (M % MOE_TC_TILE or tuple(c.shape) != (M, N) or w.shape[2] != K or not w.is_contiguous()
+            or tile_expert.numel() < M // MOE_TC_TILE):
+        raise KernelError("gemm_tc_grouped: sizes do not fit")
+    _check(lib().cretif_gemm_tc_grouped(
+        _p(a), _p(w), _p(c), M, N, K, _rows(a, "a"), K, _rows(c, "c"), E, _p(tile_expert),
+        _p(used), _p(fault_word(a.device)), _stream()), "gemm_tc_grouped")
+
+
+def moe_combine(rows, place, top: int, y, wts=None) -> None:
+    """y[t] = the sum of the token's ``top`` rows of ``rows`` (float32), in their order, each
+    times its weight when ``wts`` is given; ``place`` None: the rows are in the pairs' own
+    order."""
     _need(rows, "rows", torch.float32, 2); _need(y, "y", torch.float32, 2)
     if place is not None:
         _need(place, "place", torch.int32)
@@ -584,8 +658,8 @@ def moe_combine(rows, place, top: int, y) -> None:
     if (rows.shape[1] != H or (place is not None and place.numel() != T * top)
             or rows.shape[0] < T * top or not y.is_contiguous()):
         raise KernelError("moe_combine: sizes do not fit")
-    _check(lib().cretif_moe_combine(_p(rows), _rows(rows, "rows"), _p(place), top, _p(y), T, H,
-                                    _stream()), "moe_combine")
+    _check(lib().cretif_moe_combine(_p(rows), _rows(rows, "rows"), _p(place), top, _p(wts), _p(y),
+                                    T, H, _stream()), "moe_combine")
 
 
 # ------------------------------------------------------------------ attention

@@ -78,6 +78,15 @@ class RoutedExperts(Part):
         self.w_gu = self._matrix(torch.stack(
             [torch.cat([tensors[f"gate{e}"], tensors[f"up{e}"]], dim=0) for e in range(E)]))
         self.w_down = self._matrix(torch.stack([tensors[f"down{e}"] for e in range(E)]))
+        # for the tensor-core grouped product, whose epilogue applies SiLU·mul: gate and up
+        # rows of an expert alternate in blocks of 64 (as the dense feed-forward stores them)
+        self.w_gu_blocks = None
+        F = self.inter
+        if self.dtype == torch.bfloat16 and F % 64 == 0 and self.hidden_size % 8 == 0:
+            self.w_gu_blocks = self._matrix(torch.stack([torch.stack(
+                [tensors[f"gate{e}"].reshape(F // 64, 64, -1),
+                 tensors[f"up{e}"].reshape(F // 64, 64, -1)], dim=1).reshape(2 * F, -1)
+                for e in range(E)]))
 
     def forward(self, x, ctx):
         T, H = x.shape
@@ -87,14 +96,30 @@ class RoutedExperts(Part):
         wts = torch.empty((T, self.top), dtype=torch.float32, device=dev)
         ops.moe_route(x, self.router, self.top, ids, wts, renorm=self.renorm)
         on_input = self.weight_on == "input"
-        act = torch.empty((P, self.inter), dtype=self.dtype, device=dev)
-        rows = torch.empty((P, H), dtype=torch.float32, device=dev)
         y = torch.empty((T, H), dtype=torch.float32, device=dev)
         if P <= FEW_PAIRS and not few_pairs_off():
             # a handful of pairs: every pair streams its expert's rows, nothing is sorted
+            act = torch.empty((P, self.inter), dtype=self.dtype, device=dev)
+            rows = torch.empty((P, H), dtype=torch.float32, device=dev)
             ops.moe_gemv(x, self.w_gu, act, self.top, 0, 1 if on_input else 0, ids, wts)
             ops.moe_gemv(act, self.w_down, rows, self.top, 1, 0 if on_input else 2, ids, wts)
             ops.moe_combine(rows, None, self.top, y)
+            return y
+        if self.w_gu_blocks is not None and ops.moe_tc_supported(x, self.w_gu_blocks, self.w_down):
+            # many pairs, bfloat16: the tcgen05 product in its grouped mode over rows sorted
+            # into whole 128-row tiles per expert; the router weight goes into the gathered rows
+            tiles = ops.moe_tc_tiles(P, self.E)
+            idx = torch.empty(P + tiles + 1, dtype=torch.int32, device=dev)
+            place, tile_expert, used = idx[:P], idx[P:P + tiles], idx[P + tiles:]
+            ops.moe_group_padded(ids, self.E, place, tile_expert, used)
+            rows_pad = tiles * ops.MOE_TC_TILE
+            xs = torch.empty((rows_pad, H), dtype=self.dtype, device=dev)
+            ops.moe_gather_rows(x, xs, place, wts if on_input else None, self.top)
+            act = torch.empty((rows_pad, self.inter), dtype=self.dtype, device=dev)
+            ops.gemm_tc_silu_grouped(xs, self.w_gu_blocks, act, tile_expert, used)
+            rows = torch.empty((rows_pad, H), dtype=torch.float32, device=dev)
+            ops.gemm_tc_grouped(act, self.w_down, rows, tile_expert, used)
+            ops.moe_combine(rows, place, self.top, y, wts=None if on_input else wts)
             return y
         tiles = ops.moe_max_tiles(P, self.E)
         idx = torch.empty(self.E + 1 + 2 * P + 2 * tiles, dtype=torch.int32, device=dev)
@@ -103,6 +128,8 @@ class RoutedExperts(Part):
         tile_expert, tile_row0 = idx[self.E + 1 + 2 * P:self.E + 1 + 2 * P + tiles], \
             idx[self.E + 1 + 2 * P + tiles:]
         ops.moe_group(ids, self.E, offsets, place, order, tile_expert, tile_row0)
+        act = torch.empty((P, self.inter), dtype=self.dtype, device=dev)
+        rows = torch.empty((P, H), dtype=torch.float32, device=dev)
         ops.moe_gemm(x, self.w_gu, act, self.top, 0, 1 if on_input else 0, wts, order, offsets,
                      tile_expert, tile_row0)
         ops.moe_gemm(act, self.w_down, rows, self.top, 1, 0 if on_input else 2, wts, order,
@@ -111,5 +138,6 @@ class RoutedExperts(Part):
         return y
 
     def weight_bytes(self):
+        # (the blocked copy of gate|up serves the many-pairs path and is not counted twice)
         return ((self.w_gu.numel() + self.w_down.numel()) * self.w_down.element_size()
                 + 4 * self.router.numel())

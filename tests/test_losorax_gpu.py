@@ -406,6 +406,8 @@ def test_general_delta_rule_kernels_in_pieces(H, d, e, R):
 
 @pytest.mark.parametrize("T,H,F,E,top", [(1, 64, 32, 6, 2), (70, 96, 40, 5, 3), (9, 48, 48, 1, 1),
                                          (8, 100, 36, 9, 4), (3, 70, 30, 4, 2),
+                                         (300, 64, 64, 7, 2), (1000, 128, 192, 12, 3),
+                                         (40, 256, 128, 33, 4), (9, 64, 64, 3, 2),
                                          (300, 40, 24, 7, 2), (130, 64, 100, 12, 1),
                                          (33, 72, 20, 40, 4)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -435,11 +437,16 @@ def test_routed_experts_kernels(T, H, F, E, top, dtype):
     for simt, sorted_tiles in ways:
         ops.moe_simt_only(simt)
         experts.few_pairs_off(sorted_tiles)
+        before = ops.variant_counts()
         try:
             got = part.forward(x.cuda(), None)
         finally:
             ops.moe_simt_only(False)
             experts.few_pairs_off(False)
+        after = ops.variant_counts()
+        ran_tc = sum(after[k] - before[k] for k in ("tc64", "tc128", "tc256"))
+        # bfloat16 experts whose width is a multiple of 64 take the tcgen05 grouped products
+        assert ran_tc == (2 if (not simt and sorted_tiles and F % 64 == 0 and H % 8 == 0) else 0)
         err = (got.cpu().double() - want).abs().max(dim=1).values / want.abs().max()
         # (in bfloat16 the activation between the products is rounded)
         assert err.max() <= tol, (simt, sorted_tiles, float(err.max()))
