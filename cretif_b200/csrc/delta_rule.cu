@@ -460,9 +460,10 @@ extern "C" int cretif_delta_recurrence(const float* prep, int ldp, const float* 
 namespace cretif {
 
 constexpr int kGenChunk = 8;
+constexpr int kGenRows = 16;
 
 // proj row: [r (H d) | k (H d) | v (H e) | gate (H e) | a (H d) | w1 (R)]
-// prep row: [u (H d) | b (H d) | w (H d)];  z row: W2 tanh(w1), [H d]
+// prep row: [u (H d) | -b (H d) | w (H d)];  z row: W2 tanh(w1), [H d]
 __global__ void __launch_bounds__(kPrepWarps * 32)
 general_delta_prepare_kernel(const float* __restrict__ proj, int ldp, float* __restrict__ prep,
                              int ldo, const float* __restrict__ a_bias,
@@ -498,7 +499,7 @@ general_delta_prepare_kernel(const float* __restrict__ proj, int ldp, float* __r
     const float rate = 1.0f / (1.0f + expf(-(av[m] + a_bias[c])));
     const float decay = expf(-decay_scale / (1.0f + expf(-(zv[m] + w0[c]))));
     out[c] = u;
-    out[(size_t)H * d + c] = rate * u;
+    out[(size_t)H * d + c] = -rate * u;          // stored negative: the recurrence adds it
     out[(size_t)2 * H * d + c] = decay;
   }
 }
@@ -533,11 +534,13 @@ general_delta_recurrence_kernel(const float* __restrict__ proj, int ldp,
   const int tid = threadIdx.x, part = tid % P, jl = tid / P, j = col0 + jl;
   const bool active = jl < ecols;
   float* M = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e;
-  float S[DREG];
+  // the lane's rows in pairs: the arithmetic below is two-wide (one instruction, two rows)
+  float2 S[DREG / 2];
 #pragma unroll
-  for (int r = 0; r < DREG; ++r) {
-    const int i = part * DREG + r;
-    S[r] = (active && i < d) ? M[(size_t)i * e + j] : 0.f;
+  for (int r = 0; r < DREG / 2; ++r) {
+    const int i = part * DREG + 2 * r;
+    S[r].x = (active && i < d) ? M[(size_t)i * e + j] : 0.f;
+    S[r].y = (active && i + 1 < d) ? M[(size_t)(i + 1) * e + j] : 0.f;
   }
   const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
   for (int idx = tid; idx < 2 * stage_floats; idx += blockDim.x) sm[idx] = 0.f;
@@ -547,7 +550,7 @@ general_delta_recurrence_kernel(const float* __restrict__ proj, int ldp,
     float* base = sm + s * stage_floats;
     float* vs = base + 5 * kGenChunk * dpad;
     const int n = min(kGenChunk, t1 - c0);
-    // vector x of token tt, rows i..: from the projection (r, k) or the prepared row (u, b, w)
+    // vector x of token tt, rows i..: from the projection (r, k) or the prepared row (u, -b, w)
     auto src = [&](int x, int tt, int i) -> const float* {
       return x < 2 ? proj + (size_t)(c0 + tt) * ldp + (size_t)x * Hd + (size_t)h * d + i
                    : prep + (size_t)(c0 + tt) * ldq + (size_t)(x - 2) * Hd + (size_t)h * d + i;
@@ -589,6 +592,7 @@ general_delta_recurrence_kernel(const float* __restrict__ proj, int ldp,
     const float* base = sm + s * stage_floats;
     const float* vs = base + 5 * kGenChunk * dpad;
     float* orow = o_raw + (size_t)c0 * H * e + (size_t)h * e + j;
+    float v_next = active ? vs[jl] : 0.f;
     for (int tt = 0; tt < n; ++tt) {
       const int off = tt * dpad + part * kSlice;
       const float4* r4 = reinterpret_cast<const float4*>(base + off);
@@ -596,43 +600,47 @@ general_delta_recurrence_kernel(const float* __restrict__ proj, int ldp,
       const float4* u4 = reinterpret_cast<const float4*>(base + 2 * kGenChunk * dpad + off);
       const float4* b4 = reinterpret_cast<const float4*>(base + 3 * kGenChunk * dpad + off);
       const float4* w4 = reinterpret_cast<const float4*>(base + 4 * kGenChunk * dpad + off);
-      const float vj = active ? vs[tt * ecols + jl] : 0.f;
-      // what the old state holds along the unit key, in four chains
-      float x0 = 0.f, x1 = 0.f, x2 = 0.f, x3 = 0.f;
+      const float vj = v_next;
+      if (tt + 1 < n) v_next = active ? vs[(tt + 1) * ecols + jl] : 0.f;
+      // what the old state holds along the unit key, in two two-wide chains
+      float2 xa = make_float2(0.f, 0.f), xb = make_float2(0.f, 0.f);
 #pragma unroll
       for (int q = 0; q < DREG / 4; ++q) {
         const float4 u = u4[q];
-        x0 = fmaf(S[4 * q], u.x, x0);
-        x1 = fmaf(S[4 * q + 1], u.y, x1);
-        x2 = fmaf(S[4 * q + 2], u.z, x2);
-        x3 = fmaf(S[4 * q + 3], u.w, x3);
+        xa = __ffma2_rn(S[2 * q], make_float2(u.x, u.y), xa);
+        xb = __ffma2_rn(S[2 * q + 1], make_float2(u.z, u.w), xb);
       }
-      float x = (x0 + x1) + (x2 + x3);
+      float x = (xa.x + xa.y) + (xb.x + xb.y);
       for (int o = P >> 1; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-      // decay, removal and write on every row the lane holds, then the read-out's chains
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      // decay, removal (the prepared vector is minus a * u) and write on every row the lane
+      // holds, then the read-out's chains; two rows an instruction
+      const float2 x2 = make_float2(x, x), v2 = make_float2(vj, vj);
+      float2 aa = make_float2(0.f, 0.f), ab = make_float2(0.f, 0.f);
 #pragma unroll
       for (int q = 0; q < DREG / 4; ++q) {
-        const float4 w = w4[q], bb = b4[q], kk = k4[q], rr = r4[q];
-        S[4 * q] = fmaf(kk.x, vj, fmaf(-bb.x, x, w.x * S[4 * q]));
-        S[4 * q + 1] = fmaf(kk.y, vj, fmaf(-bb.y, x, w.y * S[4 * q + 1]));
-        S[4 * q + 2] = fmaf(kk.z, vj, fmaf(-bb.z, x, w.z * S[4 * q + 2]));
-        S[4 * q + 3] = fmaf(kk.w, vj, fmaf(-bb.w, x, w.w * S[4 * q + 3]));
-        a0 = fmaf(S[4 * q], rr.x, a0);
-        a1 = fmaf(S[4 * q + 1], rr.y, a1);
-        a2 = fmaf(S[4 * q + 2], rr.z, a2);
-        a3 = fmaf(S[4 * q + 3], rr.w, a3);
+        const float4 w = w4[q], nb = b4[q], kk = k4[q], rr = r4[q];
+        float2 lo = __fmul2_rn(S[2 * q], make_float2(w.x, w.y));
+        float2 hi = __fmul2_rn(S[2 * q + 1], make_float2(w.z, w.w));
+        lo = __ffma2_rn(make_float2(nb.x, nb.y), x2, lo);
+        hi = __ffma2_rn(make_float2(nb.z, nb.w), x2, hi);
+        lo = __ffma2_rn(make_float2(kk.x, kk.y), v2, lo);
+        hi = __ffma2_rn(make_float2(kk.z, kk.w), v2, hi);
+        S[2 * q] = lo;
+        S[2 * q + 1] = hi;
+        aa = __ffma2_rn(lo, make_float2(rr.x, rr.y), aa);
+        ab = __ffma2_rn(hi, make_float2(rr.z, rr.w), ab);
       }
-      float acc = (a0 + a1) + (a2 + a3);
+      float acc = (aa.x + aa.y) + (ab.x + ab.y);
       for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (active && part == 0) orow[(size_t)tt * H * e] = acc;
     }
   }
   if (write_state) {
 #pragma unroll
-    for (int r = 0; r < DREG; ++r) {
-      const int i = part * DREG + r;
-      if (active && i < d) M[(size_t)i * e + j] = S[r];
+    for (int r = 0; r < DREG / 2; ++r) {
+      const int i = part * DREG + 2 * r;
+      if (active && i < d) M[(size_t)i * e + j] = S[r].x;
+      if (active && i + 1 < d) M[(size_t)(i + 1) * e + j] = S[r].y;
     }
   }
 }
@@ -721,10 +729,12 @@ extern "C" int cretif_general_delta_recurrence(
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  // the same plan as cretif_delta_recurrence: up to 32 rows a lane, a head's columns in slices
-  // while the (sequence, head) pairs alone do not fill the chip twice over
+  // the plan of cretif_delta_recurrence with up to 16 rows a lane (a token's update is five
+  // vectors here, not two: more lanes a column halve a lane's instructions and double the warps
+  // that hide each other's waits), a head's columns in slices while the (sequence, head) pairs
+  // alone do not fill the chip twice over
   int P = 1;
-  while (P < 32 && (d + P - 1) / P > 32) P *= 2;
+  while (P < 32 && (d + P - 1) / P > kGenRows) P *= 2;
   int ecols = e;
   while ((long long)B * H * (e / ecols) < 2LL * sm_count && ecols % 2 == 0 && ecols / 2 >= 32)
     ecols /= 2;
@@ -732,7 +742,7 @@ extern "C" int cretif_general_delta_recurrence(
   while (ecols * P > 1024 && P > 1) P /= 2;
   if (ecols * P > 1024) return kBadArgument;
   const int rows = (d + P - 1) / P;
-  if (rows > 128) return kBadArgument;
+  if (rows > 32) return kBadArgument;               // head sizes beyond 1024
   cudaStream_t st = (cudaStream_t)stream;
   int rc;
 #define CRETIF_GDELTA(DREG)                                                                     \
@@ -740,9 +750,7 @@ extern "C" int cretif_general_delta_recurrence(
                        B, H, d, e, P, ecols, o_raw, write_state, st)
   if (rows <= 8) rc = CRETIF_GDELTA(8);
   else if (rows <= 16) rc = CRETIF_GDELTA(16);
-  else if (rows <= 32) rc = CRETIF_GDELTA(32);
-  else if (rows <= 64) rc = CRETIF_GDELTA(64);
-  else rc = CRETIF_GDELTA(128);
+  else rc = CRETIF_GDELTA(32);
 #undef CRETIF_GDELTA
   if (rc) return rc;
   const long long items = (long long)T * H;
