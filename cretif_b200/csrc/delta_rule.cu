@@ -714,6 +714,16 @@ extern "C" int cretif_tanh_cols(const float* in, int ld, void* out, int out_dt, 
 
 // per_head_weight: norm_w holds H * e numbers (else e, shared by the heads); gate_sigmoid: the
 // gate is the logistic function of its projection (else SiLU).
+// Fewest columns of a head's matrix a CTA takes (a test hook and tuning aid).  Measured at 16
+// heads of 128 x 128 over 2,048 tokens of one sequence: 32 columns 1.81 ms, 16 1.92, 8 2.47,
+// 4 3.57 (every CTA stages all five vectors of a token whatever its columns).
+static int g_gen_min_cols = 32;
+extern "C" int cretif_general_delta_min_cols(int n) {
+  const int was = g_gen_min_cols;
+  if (n >= 1) g_gen_min_cols = n;
+  return was;
+}
+
 extern "C" int cretif_general_delta_recurrence(
     const float* proj, int ldp, const float* prep, int ldq, const float* gate, int ldg,
     float* state, long long state_stride, const int* cu_seqlens, const int* seq_slot, int B, int H,
@@ -736,7 +746,8 @@ extern "C" int cretif_general_delta_recurrence(
   int P = 1;
   while (P < 32 && (d + P - 1) / P > kGenRows) P *= 2;
   int ecols = e;
-  while ((long long)B * H * (e / ecols) < 2LL * sm_count && ecols % 2 == 0 && ecols / 2 >= 32)
+  while ((long long)B * H * (e / ecols) < 2LL * sm_count && ecols % 2 == 0 &&
+         ecols / 2 >= g_gen_min_cols)
     ecols /= 2;
   while (ecols * P > 1024 && ecols % 2 == 0 && ecols > 1) ecols /= 2;
   while (ecols * P > 1024 && P > 1) P /= 2;
