@@ -119,6 +119,8 @@ int cretif_general_delta_recurrence(const float* proj, int ldp, const float* pre
 // Routed experts (moe.cu).
 int cretif_moe_route(const void* x, int x_dt, int ldx, const float* router_w, int E, int H,
                      int top, int renorm, int* ids, float* wts, int T, void* stream);
+int cretif_moe_topk(const float* logits, int ld, int E, int top, int renorm, int* ids, float* wts,
+                    int T, void* stream);
 int cretif_moe_group(const int* ids, int P, int E, int* offsets, int* place, int* order,
                      int* tile_expert, int* tile_row0, int max_tiles, void* stream);
 int cretif_moe_gemm(const void* A, int a_dt, int lda, const void* W, int w_dt, void* C, int ldc,

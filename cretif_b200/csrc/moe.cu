@@ -37,6 +37,55 @@ namespace {
 constexpr int kTile = 64;
 constexpr int kMaxExpertsPerLane = 8;            // E <= 256
 
+// Warp-wide: the `top` largest of E logits (ties: the lower index), their logistic scores as
+// weights (divided by their sum with renorm), written for token t.
+__device__ __forceinline__ void select_top(const float* logits, int E, int top, int renorm,
+                                           int* __restrict__ ids, float* __restrict__ wts, int t,
+                                           int lane) {
+  float z[kMaxExpertsPerLane];
+#pragma unroll
+  for (int m = 0; m < kMaxExpertsPerLane; ++m) {
+    const int e = lane + 32 * m;
+    z[m] = e < E ? logits[e] : -INFINITY;
+  }
+  float total = 0.f;
+  float my_w = 0.f;
+  int my_id = 0;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int m = 0; m < kMaxExpertsPerLane; ++m) {
+      const int e = lane + 32 * m;
+      if (e < E && z[m] > best) { best = z[m]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int m = 0; m < kMaxExpertsPerLane; ++m)
+        if (m == (best_e >> 5)) z[m] = -INFINITY;
+    }
+    const float s = 1.0f / (1.0f + expf(-best));
+    total += s;
+    if (lane == k % 32 && k < 32) { my_w = s; my_id = best_e; }
+    if (k >= 32 && lane == 0) {                  // more than 32 choices: written one by one
+      ids[(size_t)t * top + k] = best_e;
+      wts[(size_t)t * top + k] = s;
+    }
+  }
+  if (lane < top && lane < 32) {
+    ids[(size_t)t * top + lane] = my_id;
+    wts[(size_t)t * top + lane] = renorm ? my_w / total : my_w;
+  }
+  if (renorm && top > 32 && lane == 0)
+    for (int k = 32; k < top; ++k) wts[(size_t)t * top + k] /= total;
+}
+
 // A CTA per token: its sixteen warps take the experts in turn (a dot product each, every load of
 // a row in flight at once where the width is a multiple of four), leave the logits in shared
 // memory, and warp 0 picks the `top` largest.
@@ -80,48 +129,16 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const float* __restrict__ wr,
   }
   __syncthreads();
   if (warp != 0) return;
-  float z[kMaxExpertsPerLane];
-#pragma unroll
-  for (int m = 0; m < kMaxExpertsPerLane; ++m) {
-    const int e = lane + 32 * m;
-    z[m] = e < E ? logits[e] : -INFINITY;
-  }
-  float total = 0.f;
-  float my_w = 0.f;
-  int my_id = 0;
-  for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
-    int best_e = 0x7fffffff;
-#pragma unroll
-    for (int m = 0; m < kMaxExpertsPerLane; ++m) {
-      const int e = lane + 32 * m;
-      if (e < E && z[m] > best) { best = z[m]; best_e = e; }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-    }
-    if ((best_e & 31) == lane) {
-#pragma unroll
-      for (int m = 0; m < kMaxExpertsPerLane; ++m)
-        if (m == (best_e >> 5)) z[m] = -INFINITY;
-    }
-    const float s = 1.0f / (1.0f + expf(-best));
-    total += s;
-    if (lane == k % 32 && k < 32) { my_w = s; my_id = best_e; }
-    if (k >= 32 && lane == 0) {                  // more than 32 choices: written one by one
-      ids[(size_t)t * top + k] = best_e;
-      wts[(size_t)t * top + k] = s;
-    }
-  }
-  if (lane < top && lane < 32) {
-    ids[(size_t)t * top + lane] = my_id;
-    wts[(size_t)t * top + lane] = renorm ? my_w / total : my_w;
-  }
-  if (renorm && top > 32 && lane == 0)
-    for (int k = 32; k < top; ++k) wts[(size_t)t * top + k] /= total;
+  select_top(logits, E, top, renorm, ids, wts, t, lane);
+}
+
+// The same choice from logits that a matrix product left in memory: a warp per token.
+__global__ void __launch_bounds__(256)
+moe_topk_kernel(const float* __restrict__ logits, int ld, int E, int top, int renorm,
+                int* __restrict__ ids, float* __restrict__ wts, int T) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  select_top(logits + (size_t)t * ld, E, top, renorm, ids, wts, t, threadIdx.x & 31);
 }
 
 // tile: rows of a tile; padded: every expert's rows start at a multiple of `tile` (the sorted
@@ -497,6 +514,16 @@ extern "C" int cretif_moe_route(const void* x, int x_dt, int ldx, const float* r
         (const __nv_bfloat16*)x, ldx, router_w, E, H, top, renorm, ids, wts, vec);
   else
     return kBadDType;
+  return launch_status();
+}
+
+// ids/wts from logits [T, ld >= E] that a matrix product computed.
+extern "C" int cretif_moe_topk(const float* logits, int ld, int E, int top, int renorm, int* ids,
+                               float* wts, int T, void* stream) {
+  if (T <= 0) return kOk;
+  if (E <= 0 || E > kMaxExperts || top <= 0 || top > E || ld < E) return kBadArgument;
+  moe_topk_kernel<<<(unsigned)((T + 7) / 8), 256, 0, (cudaStream_t)stream>>>(logits, ld, E, top,
+                                                                             renorm, ids, wts, T);
   return launch_status();
 }
 

@@ -523,6 +523,18 @@ def moe_route(x, router_w, top: int, ids, wts, renorm: bool = False) -> None:
                                   int(renorm), _p(ids), _p(wts), T, _stream()), "moe_route")
 
 
+def moe_topk(logits, top: int, ids, wts, renorm: bool = False) -> None:
+    """``moe_route``'s choice from router logits [T, E] (float32) that a matrix product left."""
+    _need(logits, "logits", torch.float32, 2); _need(ids, "ids", torch.int32, 2)
+    _need(wts, "wts", torch.float32, 2)
+    T, E = logits.shape
+    if (tuple(ids.shape) != (T, top) or tuple(wts.shape) != (T, top) or not ids.is_contiguous()
+            or not wts.is_contiguous() or not 0 < top <= E or E > 256):
+        raise KernelError("moe_topk: sizes do not fit")
+    _check(lib().cretif_moe_topk(_p(logits), _rows(logits, "logits"), E, top, int(renorm), _p(ids),
+                                 _p(wts), T, _stream()), "moe_topk")
+
+
 def moe_group(ids, experts: int, offsets, place, order, tile_expert, tile_row0) -> None:
     """Sort the (token, choice) pairs by expert: ``offsets`` [E + 1], ``place`` [P] (a pair's
     row in the sorted list), ``order`` [P] (its inverse) and the list of 64-row tiles."""

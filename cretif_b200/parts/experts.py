@@ -26,6 +26,8 @@ from .base import Part, register_part
 # expert's matrices once per pair; beyond it the pairs are sorted and an expert's rows share a
 # tile's read.
 FEW_PAIRS = 32
+# Steps of more tokens than this compute the router's logits with the library's matrix product.
+ROUTE_BY_PRODUCT = 64
 _few_pairs_off = False
 
 
@@ -74,6 +76,11 @@ class RoutedExperts(Part):
     def load(self, tensors):
         E = self.E
         self.router = self._vector32(tensors["router"])            # 32-bit logits
+        # Many tokens: the logits are a matrix product (32-bit sums of exact products) whenever
+        # the stored router is exact in the compute type, which a bfloat16 checkpoint's is.
+        self.router_matrix = self._matrix(tensors["router"])
+        if not torch.equal(self.router_matrix.float(), self.router):
+            self.router_matrix = None
         # per expert [gate rows | up rows], all experts in one tensor
         self.w_gu = self._matrix(torch.stack(
             [torch.cat([tensors[f"gate{e}"], tensors[f"up{e}"]], dim=0) for e in range(E)]))
@@ -94,7 +101,12 @@ class RoutedExperts(Part):
         P = T * self.top
         ids = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         wts = torch.empty((T, self.top), dtype=torch.float32, device=dev)
-        ops.moe_route(x, self.router, self.top, ids, wts, renorm=self.renorm)
+        if T > ROUTE_BY_PRODUCT and self.router_matrix is not None:
+            from .linear import linear
+            logits = linear(x, self.router_matrix, out_dtype=torch.float32)
+            ops.moe_topk(logits, self.top, ids, wts, renorm=self.renorm)
+        else:
+            ops.moe_route(x, self.router, self.top, ids, wts, renorm=self.renorm)
         on_input = self.weight_on == "input"
         y = torch.empty((T, H), dtype=torch.float32, device=dev)
         if P <= FEW_PAIRS and not few_pairs_off():
