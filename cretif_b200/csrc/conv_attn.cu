@@ -10,8 +10,9 @@
 //   q head:  x / sqrt(mean(x^2) + eps) * (1 + coef * ln(floor((pos + 1) / every) + 1))  -> q_out
 //   k head:  x / sqrt(mean(x^2) + eps)                                                  -> key cache
 //   v head:  x                                                                          -> value cache
-// A warp per head of a token; a head's channels stay in the lanes' registers between the
-// convolution and the scaling (head sizes up to 512).  The saved inputs are brought up to date
+// A warp per head of a token (with many tokens, eight warps per token that take its heads in
+// turn); a head's channels stay in the lanes' registers between the convolution and the scaling
+// (head sizes up to 512).  The saved inputs are brought up to date
 // afterwards by delta_conv_state (delta_rule.cu), which is the same for every convolved mixer.
 #include "api.h"
 #include "common.cuh"
@@ -37,14 +38,25 @@ conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
                                unsigned int* __restrict__ fault) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
-  const int unit = blockIdx.y * kCvWarps + warp;
-  if (unit >= nh + 2 * nkv) return;
+  const int units = nh + 2 * nkv;
+  // what the token's heads share is read once; a warp then takes heads in turn (with many
+  // tokens a CTA's eight warps take all of a token's heads: the chain of index loads is paid
+  // once per warp and there are few enough warps to be resident together)
   const int b = tok_seq[t];
   const int pos = tok_pos[t];
   const int lt = pos - seq_start[b];             // tokens of this sequence before t in the step
   const int slot = seq_slot[b];
   const float* st = conv_state + (size_t)slot * state_stride;
   const float* row = proj + (size_t)t * ldp;
+  int blk = 0;
+  if (nkv > 0 && write_cache) {
+    blk = table[(size_t)slot * table_stride + pos / bt];
+    if (blk < 0) {
+      if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(fault, kFaultBlockTable);
+    }
+  }
+  const float gain =
+      gain_every > 0 ? 1.0f + gain_coef * logf((float)((pos + 1) / gain_every + 1)) : 1.0f;
   auto conv = [&](int c) {
     float acc = 0.f;
 #pragma unroll 4
@@ -56,45 +68,38 @@ conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
     }
     return acc;
   };
-  const bool is_q = unit < nh, is_k = !is_q && unit < nh + nkv;
-  const int n = (is_q || is_k) ? hd : vd;
-  const int c0 = is_q ? unit * hd : is_k ? nh * hd + (unit - nh) * hd
-                                         : (nh + nkv) * hd + (unit - nh - nkv) * vd;
-  float val[NCH];
-  float ss = 0.f;
-#pragma unroll
-  for (int m = 0; m < NCH; ++m) {
-    const int i = lane + 32 * m;
-    val[m] = i < n ? conv(c0 + i) : 0.f;
-    ss += val[m] * val[m];
-  }
-  float f = 1.f;
-  if (is_q || is_k) {
-    ss = warp_sum(ss);
-    f = 1.0f / sqrtf(ss / (float)hd + eps);
-  }
-  if (is_q) {
-    if (gain_every > 0) f *= 1.0f + gain_coef * logf((float)((pos + 1) / gain_every + 1));
-    T* q = q_out + (size_t)t * ldq + (size_t)unit * hd;
+  for (int unit = blockIdx.y * kCvWarps + warp; unit < units; unit += gridDim.y * kCvWarps) {
+    const bool is_q = unit < nh, is_k = !is_q && unit < nh + nkv;
+    const int n = (is_q || is_k) ? hd : vd;
+    const int c0 = is_q ? unit * hd : is_k ? nh * hd + (unit - nh) * hd
+                                           : (nh + nkv) * hd + (unit - nh - nkv) * vd;
+    float val[NCH];
+    float ss = 0.f;
 #pragma unroll
     for (int m = 0; m < NCH; ++m) {
       const int i = lane + 32 * m;
-      if (i < n) q[i] = from_float<T>(val[m] * f);
+      val[m] = i < n ? conv(c0 + i) : 0.f;
+      ss += val[m] * val[m];
     }
-    return;
-  }
-  if (!write_cache) return;
-  const int blk = table[(size_t)slot * table_stride + pos / bt];
-  if (blk < 0) {
-    if (lane == 0) atomicOr(fault, kFaultBlockTable);
-    return;
-  }
-  const int kvh = is_k ? unit - nh : unit - nh - nkv;
-  T* dst = (is_k ? kc : vc) + (((size_t)blk * nkv + kvh) * bt + (pos % bt)) * n;
+    float f = 1.f;
+    if (is_q || is_k) {
+      ss = warp_sum(ss);
+      f = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
+    T* dst;
+    if (is_q) {
+      f *= gain;
+      dst = q_out + (size_t)t * ldq + (size_t)unit * hd;
+    } else {
+      if (!write_cache || blk < 0) continue;
+      const int kvh = is_k ? unit - nh : unit - nh - nkv;
+      dst = (is_k ? kc : vc) + (((size_t)blk * nkv + kvh) * bt + (pos % bt)) * n;
+    }
 #pragma unroll
-  for (int m = 0; m < NCH; ++m) {
-    const int i = lane + 32 * m;
-    if (i < n) dst[i] = from_float<T>(val[m] * f);
+    for (int m = 0; m < NCH; ++m) {
+      const int i = lane + 32 * m;
+      if (i < n) dst[i] = from_float<T>(val[m] * f);
+    }
   }
 }
 }  // namespace
@@ -115,7 +120,8 @@ extern "C" int cretif_conv_headnorm_kv_append(
   if (ldp < (nh + nkv) * hd + nkv * vd) return kBadArgument;
   if (taps > 1 && !conv_state) return kBadArgument;
   const int units = nh + 2 * nkv;
-  dim3 grid(T, (units + kCvWarps - 1) / kCvWarps);
+  // few tokens: a warp per head, spread over CTAs; many: a CTA per token walks its heads
+  dim3 grid(T, T >= 256 ? 1 : (units + kCvWarps - 1) / kCvWarps);
   if (grid.y > 65535) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
   const int widest = nkv > 0 && vd > hd ? vd : hd;

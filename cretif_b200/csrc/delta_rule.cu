@@ -460,7 +460,6 @@ extern "C" int cretif_delta_recurrence(const float* prep, int ldp, const float* 
 namespace cretif {
 
 constexpr int kGenChunk = 8;
-constexpr int kGenRows = 16;
 
 // proj row: [r (H d) | k (H d) | v (H e) | gate (H e) | a (H d) | w1 (R)]
 // prep row: [u (H d) | -b (H d) | w (H d)];  z row: W2 tanh(w1), [H d]
@@ -718,6 +717,14 @@ extern "C" int cretif_tanh_cols(const float* in, int ld, void* out, int out_dt, 
 // heads of 128 x 128 over 2,048 tokens of one sequence: 32 columns 1.81 ms, 16 1.92, 8 2.47,
 // 4 3.57 (every CTA stages all five vectors of a token whatever its columns).
 static int g_gen_min_cols = 32;
+// Rows of a column that a lane holds: 0 = by how full the chip is (below), else 8, 16 or 32 (a
+// test hook and tuning aid).
+static int g_gen_rows = 0;
+extern "C" int cretif_general_delta_rows(int n) {
+  const int was = g_gen_rows;
+  if (n == 0 || n == 8 || n == 16 || n == 32) g_gen_rows = n;
+  return was;
+}
 extern "C" int cretif_general_delta_min_cols(int n) {
   const int was = g_gen_min_cols;
   if (n >= 1) g_gen_min_cols = n;
@@ -739,12 +746,19 @@ extern "C" int cretif_general_delta_recurrence(
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  // the plan of cretif_delta_recurrence with up to 16 rows a lane (a token's update is five
-  // vectors here, not two: more lanes a column halve a lane's instructions and double the warps
-  // that hide each other's waits), a head's columns in slices while the (sequence, head) pairs
-  // alone do not fill the chip twice over
+  // The plan of cretif_delta_recurrence, with the rows a lane holds chosen by how full the chip
+  // is: a token's update is five vectors here, not two, and while there are fewer CTAs than SMs
+  // more lanes a column shorten a lane's chain and add warps that hide each other's waits; with
+  // the chip full, fewer shuffles win.  Measured at 16 heads of 128 x 128 over 2,048 tokens, ms:
+  // one sequence 1.47 / 1.80 / 2.26 at 8 / 16 / 32 rows a lane, eight sequences of 256 tokens
+  // 0.61 / 0.50 / 0.47.
+  int rows_max = g_gen_rows;
+  if (!rows_max) {
+    const long long ctas = (long long)B * H * ((e + 31) / 32);
+    rows_max = ctas < sm_count ? 8 : (ctas < 2LL * sm_count ? 16 : 32);
+  }
   int P = 1;
-  while (P < 32 && (d + P - 1) / P > kGenRows) P *= 2;
+  while (P < 32 && (d + P - 1) / P > rows_max) P *= 2;
   int ecols = e;
   while ((long long)B * H * (e / ecols) < 2LL * sm_count && ecols % 2 == 0 &&
          ecols / 2 >= g_gen_min_cols)
