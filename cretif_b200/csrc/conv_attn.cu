@@ -57,14 +57,31 @@ conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
   }
   const float gain =
       gain_every > 0 ? 1.0f + gain_coef * logf((float)((pos + 1) / gain_every + 1)) : 1.0f;
+  // Where tap j (0 = the oldest) of channel c comes from is the same for every channel: this
+  // step's row `back` tokens up, or the sequence's saved inputs; a base and a stride per tap.
+  constexpr int kFastTaps = 8;
+  const float* tap_base[kFastTaps];
+  int tap_stride[kFastTaps];
+#pragma unroll
+  for (int j = 0; j < kFastTaps; ++j) {
+    const int back = taps - 1 - j;                // tokens back
+    const bool here = back <= lt;
+    tap_base[j] = here ? row - (ptrdiff_t)back * ldp : st + (taps - 1) - (back - lt);
+    tap_stride[j] = here ? 1 : taps - 1;
+  }
   auto conv = [&](int c) {
     float acc = 0.f;
-#pragma unroll 4
+    const float* w = conv_w + (size_t)c * taps;
+    if (taps <= kFastTaps) {
+#pragma unroll
+      for (int j = 0; j < kFastTaps; ++j)
+        if (j < taps) acc = fmaf(w[j], tap_base[j][(size_t)c * tap_stride[j]], acc);
+      return acc;
+    }
     for (int i = taps - 1; i >= 0; --i) {        // i tokens back, the oldest first
-      const float w = conv_w[(size_t)c * taps + (taps - 1 - i)];
       const float z = i <= lt ? row[c - (ptrdiff_t)i * ldp]
                               : st[(size_t)c * (taps - 1) + (taps - 1) - (i - lt)];
-      acc = fmaf(w, z, acc);
+      acc = fmaf(w[taps - 1 - i], z, acc);
     }
     return acc;
   };

@@ -26,7 +26,8 @@ from .base import Part, register_part
 # expert's matrices once per pair; beyond it the pairs are sorted and an expert's rows share a
 # tile's read.
 FEW_PAIRS = 32
-# Steps of more tokens than this compute the router's logits with the library's matrix product.
+# Steps of more tokens than this compute the router's logits with the library's matrix product
+# (in bfloat16 every step does: the few-token product kernels stream the router once).
 ROUTE_BY_PRODUCT = 64
 _few_pairs_off = False
 
@@ -101,9 +102,10 @@ class RoutedExperts(Part):
         P = T * self.top
         ids = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         wts = torch.empty((T, self.top), dtype=torch.float32, device=dev)
-        if T > ROUTE_BY_PRODUCT and self.router_matrix is not None:
-            from .linear import linear
-            logits = linear(x, self.router_matrix, out_dtype=torch.float32)
+        if self.router_matrix is not None and (T > ROUTE_BY_PRODUCT
+                                               or self.dtype == torch.bfloat16):
+            from .linear import linear_few
+            logits = linear_few(x, self.router_matrix, out_dtype=torch.float32)
             ops.moe_topk(logits, self.top, ids, wts, renorm=self.renorm)
         else:
             ops.moe_route(x, self.router, self.top, ids, wts, renorm=self.renorm)

@@ -42,6 +42,8 @@ class WeightSpec:
 
     def fits(self, shape) -> bool:
         shape = tuple(shape)
+        if self.shape == () and shape == (1,):          # a scalar stored as one element
+            return True
         return len(shape) == len(self.shape) and all(
             a == b or (i in self.free and a > 0)
             for i, (a, b) in enumerate(zip(shape, self.shape)))

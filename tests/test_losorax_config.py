@@ -65,6 +65,9 @@ def test_sizes_that_only_the_tensors_know(tmp_path):
     _, _, spec = load_config(d)
     got = load_weights(d, *manifest(spec))
     assert got["l0.mix.rel"].shape == (20, 4) and got["l1.mix.w1"].shape == (3, 64)
+    tensors["l0.norm1.alpha"] = tensors["l0.norm1.alpha"].reshape(1)     # a scalar as [1]
+    write_model_folder(d, cfg, tensors)
+    assert load_weights(d, *manifest(spec))["l0.norm1.alpha"].numel() == 1
     tensors["l0.mix.rel"] = torch.zeros(20, 5, dtype=torch.bfloat16)     # heads are not free
     write_model_folder(d, cfg, tensors)
     with pytest.raises(CheckpointError, match="l0.mix.rel"):

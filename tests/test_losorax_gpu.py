@@ -182,7 +182,8 @@ def _gather(cache, table, positions, bt=64):
 
 
 @pytest.mark.parametrize("H,G,d,e,taps", [(4, 2, 16, 24, 3), (2, 1, 32, 16, 1), (1, 1, 8, 8, 2),
-                                          (3, 3, 12, 20, 5), (2, 1, 96, 40, 4), (4, 0, 16, 16, 3)])
+                                          (3, 3, 12, 20, 5), (2, 1, 96, 40, 4), (4, 0, 16, 16, 3),
+                                          (2, 1, 16, 16, 9), (1, 1, 160, 300, 2)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_convolution_head_norm_gain_and_cache_write_in_pieces(H, G, d, e, taps, dtype):
     from cretif_b200.csrc import ops
