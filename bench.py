@@ -326,8 +326,8 @@ def losorax_configs(z, layers):
     """name -> config.json of the models --design losorax measures: the routed feed-forward
     has half the dense one's active width (top x expert_ff), the attention has no window."""
     att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"],
-           "scale": z["dim"] ** -0.5, "conv": 4, "bias_max": 1024, "bias_rows": 32,
-           "q_temp": {"coef": 0.3, "every": 128}}
+           "scale": z["dim"] ** -0.5, "conv": 4, "bias_max": 1024, "bias_rows": 48,
+           "q_temp": {"coef": 0.25, "every": 256}}
     dlt = {"heads": z["d_heads"], "dim": z["d_dim"], "decay_rank": z["decay_rank"]}
     dense = {"kind": "dense", "ff": z["ff"]}
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]},

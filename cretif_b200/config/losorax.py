@@ -43,6 +43,8 @@ DEFAULT_MAX_POSITIONS = 1 << 20
 UNIT_EPS = 1e-6                          # under the root of the delta rule's key length
 DECAY_SCALE = math.exp(-0.5)             # the decay is exp(-DECAY_SCALE * sigmoid(.))
 SINK_SCORE = 0.0                         # the softmax's denominator has exp(0) added
+DEFAULT_BIAS_ROWS = 64                   # what the random-weights mode draws where config.json
+DEFAULT_DECAY_RANK = 32                  # is silent; a checkpoint's tensors decide
 
 
 @dataclass
@@ -171,13 +173,13 @@ def _mixer_spec(kind: str, m: Dict[str, Any], eps: float) -> PartSpec:
             "head_norm": {"eps": eps},
             "query_gain": {"coef": float(m["q_temp"]["coef"]), "every": int(m["q_temp"]["every"])},
             "distance_bias": {"name": "mix.rel", "far": float(m["bias_max"]),
-                              "rows": int(m.get("bias_rows", 32))},
+                              "rows": int(m.get("bias_rows", DEFAULT_BIAS_ROWS))},
             "fixed_sink": SINK_SCORE,
             "names": {"q": "mix.q", "k": "mix.k", "v": "mix.v", "o": "mix.o"}})
     return PartSpec("general_delta_rule", {
         "num_heads": m["heads"], "head_dim": m["dim"], "value_dim": m["dim"], "eps": eps,
         "unit_eps": UNIT_EPS, "decay_scale": DECAY_SCALE,
-        "decay_rank": int(m.get("decay_rank", 16)),
+        "decay_rank": int(m.get("decay_rank", DEFAULT_DECAY_RANK)),
         "names": {"r": "mix.r", "k": "mix.k", "v": "mix.v", "gate": "mix.g", "a": "mix.a",
                   "a_bias": "mix.a.b", "w1": "mix.w1", "w2": "mix.w2", "w0": "mix.w0",
                   "norm": "mix.norm", "o": "mix.o"}})

@@ -210,7 +210,7 @@ class Attention(Part):
                 out["v_conv"] = (conv["v"], WeightSpec((vdim, conv["taps"]), **taps))
         if params.get("distance_bias"):
             db = params["distance_bias"]
-            out["rel"] = (db["name"], WeightSpec((int(db.get("rows", 32)), params["num_heads"]),
+            out["rel"] = (db["name"], WeightSpec((int(db.get("rows", 64)), params["num_heads"]),
                                                  init=(0.0, 1.0), free=(0,)))
         if params.get("qk_norm"):
             out["q_norm"] = (params["qk_norm"]["q"], WeightSpec((q,), init=(1.0, 0.1)))

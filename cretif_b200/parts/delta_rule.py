@@ -151,7 +151,7 @@ class GeneralDeltaRule(Part):
     def weight_specs(cls, params, hidden_size):
         H, d = params["num_heads"], params["head_dim"]
         e = params.get("value_dim") or d
-        R = int(params.get("decay_rank", 16))
+        R = int(params.get("decay_rank", 32))
         n = params["names"]
         return {"r": (n["r"], WeightSpec((H * d, hidden_size))),
                 "k": (n["k"], WeightSpec((H * d, hidden_size))),
