@@ -492,7 +492,11 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
                          int ldo, const int* __restrict__ table, int table_stride,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_slot, int nh, int nkv, int hd, float scale_log2,
-                         int split, unsigned int* __restrict__ fault) {
+                         int split, unsigned int* __restrict__ fault,
+                         const float* __restrict__ sink, const float* __restrict__ bias_near,
+                         const float* __restrict__ bias_far, int n_far) {
+  // sink, bias_near [nh, n_far], bias_far [nh] (may be null): as in attn_prefill_tc_kernel; a
+  // slot keeps its head's table behind the barriers in shared memory
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -686,6 +690,16 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t o_addr = lane_addr + (uint32_t)x * kColTile + kColO;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    // the slot's bias by distance (its head's row of the table), loaded by the slot's four warps
+    float* bias_s = reinterpret_cast<float*>(smem + ((L.total - 1024 + 15) & ~15)) + x * n_far;
+    float far_b = 0.f;
+    if (bias_near) {
+      for (int i = row; i < n_far; i += kPfBQ) bias_s[i] = bias_near[(size_t)it_head[x] * n_far + i];
+      far_b = bias_far[it_head[x]];
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + x) : "memory");
+    }
+    // with a bias the scores are scaled and biased first and then taken as they are
+    const float sc_log2 = bias_near ? 1.0f : scale_log2;
     // O *= a for this thread's row (no product of the tile is in flight, see below).
     auto rescale = [&](float a) {
 #pragma unroll
@@ -718,7 +732,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
       float mx4[4];
       auto pass = [&](bool want_p, float ref) {
         const float neg_m = (ref == -INFINITY) ? 0.f : -ref;
-        const float2 scale2 = make_float2(scale_log2, scale_log2), neg2 = make_float2(neg_m, neg_m);
+        const float2 scale2 = make_float2(sc_log2, sc_log2), neg2 = make_float2(neg_m, neg_m);
         sum2[0] = sum2[1] = make_float2(0.f, 0.f);
         mx4[0] = mx4[1] = mx4[2] = mx4[3] = -INFINITY;
         // 32 scores at a time
@@ -727,6 +741,21 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
             for (int c = 0; c < 32; ++c)
               if (key0 + c0 + c > q_pos) r[c] = 0xff800000u;          // -inf
+          }
+          if (bias_near) {
+            // (32 keys that all lie n_far or more behind the tile's first row add one number)
+            if (pos_first - (key0 + c0 + 31) >= n_far) {
+#pragma unroll
+              for (int c = 0; c < 32; ++c)
+                r[c] = __float_as_uint(fmaf(__uint_as_float(r[c]), scale_log2, far_b));
+            } else {
+#pragma unroll
+              for (int c = 0; c < 32; ++c) {
+                const int n = q_pos - (key0 + c0 + c);
+                const float bv = n >= n_far ? far_b : bias_s[max(n, 0)];
+                r[c] = __float_as_uint(fmaf(__uint_as_float(r[c]), scale_log2, bv));
+              }
+            }
           }
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
@@ -759,7 +788,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           chunk(32, r1);
         }
         // the scale is positive, so the largest raw score is the largest scaled one
-        return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+        return fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc_log2;
       };
       bool again = hs == 0;
       if (!again) {
@@ -797,6 +826,7 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
     } else if (steps > 0) {
       ok = tc::mbar_wait(&pv_done[x], 0u, abort) && ok;
       float w0 = 1.0f, w1 = 0.f;             // weights of the two slots' outputs (split)
+      float m_ref = m;                       // the reference that l is relative to
       if (split) {
         ok = tc::mbar_wait(xch_full, 0u, abort) && ok;
         const float2 other = reinterpret_cast<const float2*>(smem + L.xch)[row];
@@ -804,9 +834,12 @@ attn_prefill_pair_kernel(const __grid_constant__ CUtensorMap map_q,
           const float mm = fmaxf(m, other.x);
           w0 = fast_exp2(m - mm);
           w1 = fast_exp2(other.x - mm);
+          m_ref = mm;
         }
         l = l * w0 + other.y * w1;
       }
+      // a sink: exp(sink_h) joins the row's denominator, with no key and no value
+      if (sink) l += exp2f(sink[it_head[x]] * 1.4426950408889634f - m_ref);
       tc::tc_fence_after();
       const float inv = 1.0f / l;
       w0 *= inv;
@@ -952,26 +985,29 @@ extern "C" int cretif_attn_prefill_tc_bias(const void* qkv, int ldq, int T, void
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  const bool rows_ok = g_pf_pairing != 0 && hd <= 64 && window == 0 && items <= 65535 && !sink &&
-                       !bias_near;
+  // (its two slots keep a bias table each: up to 2 x 4,096 distances beside the K/V stages)
+  const bool rows_ok = g_pf_pairing != 0 && hd <= 64 && window == 0 && items <= 65535 &&
+                       (!bias_near || n_far <= 4096);
   const bool paired = rows_ok && (g_pf_pairing == 1 ||
                                   (g_pf_pairing < 0 && 5 * pairs * nkv * B >= 7LL * sm_count));
   if (rows_ok) {
     const PpSmem P;
+    const int pair_smem = P.total + (bias_near ? 2 * n_far * 4 + 16 : 0);
     static int configured_pair = 0;
-    if (!configured_pair) {
+    if (pair_smem > configured_pair) {
       e = cudaFuncSetAttribute(attn_prefill_pair_kernel,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, P.total);
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem);
       if (e != cudaSuccess) return (int)e;
-      configured_pair = 1;
+      configured_pair = pair_smem;
     }
     cfg.gridDim = dim3(nkv, B, (unsigned)(paired ? pairs : items));
     cfg.blockDim = dim3(kPpThreads);
-    cfg.dynamicSmemBytes = P.total;
+    cfg.dynamicSmemBytes = pair_smem;
     count_variant(paired ? kVarPrefillAttnPair : kVarPrefillAttnSplit);
     e = cudaLaunchKernelEx(&cfg, attn_prefill_pair_kernel, map_q, map_k, map_v,
                            (__nv_bfloat16*)out, ldo, table, table_stride, cu_seqlens, seq_start,
-                           seq_slot, nh, nkv, hd, scale_log2, paired ? 0 : 1, fault);
+                           seq_slot, nh, nkv, hd, scale_log2, paired ? 0 : 1, fault, sink, bias_near,
+                           bias_far, n_far);
     return e == cudaSuccess ? launch_status() : (int)e;
   }
   count_variant(kVarPrefillAttn);

@@ -346,9 +346,67 @@ def test_fast_attention_kernels_with_distance_rows(H, G, d, rows, far):
         err = (out.cpu().double() - want[first:first + T]).abs().max()
         assert err <= 2e-2 * want.abs().max(), (first, T, decode, float(err))
     after = ops.variant_counts()
-    assert after["prefill_attn"] - before["prefill_attn"] == 2          # the tensor-core kernels ran
+    ran = {k: after[k] - before[k] for k in ("prefill_attn", "prefill_attn_pair",
+                                             "prefill_attn_split")}
+    assert sum(ran.values()) == 2                                       # the tensor-core kernels ran
+    # head sizes up to 64 take the kernel with a thread per row, which has the bias as well
+    assert (ran["prefill_attn"] == 0) == (d <= 64)
     assert (after["decode_cluster"] + after["decode_split"]
             - before["decode_cluster"] - before["decode_split"]) == 3
+    assert int(fault.item()) == 0
+
+
+def test_a_sink_in_the_thread_per_row_prompt_kernel():
+    """Head size 64 without a window: the prompt kernel with a thread per row and a lazy
+    reference, with a sink of any value per head (both of its forms: two query tiles a CTA, and
+    one tile split between the CTA's slots), against the formula."""
+    import plain_rigozen
+    from cretif_b200.csrc import ops
+    from cretif_b200.parts.attention import run_attention
+    from cretif_b200.parts.base import StepContext
+    g = torch.Generator().manual_seed(8)
+    S, H, G, d = 500, 4, 2, 64
+    q = torch.randn(S, H, d, generator=g).bfloat16()
+    k = torch.randn(S, G, d, generator=g).bfloat16()
+    v = torch.randn(S, G, d, generator=g).bfloat16()
+    sink = torch.randn(H, generator=g) * 2
+    want = plain_rigozen.windowed_softmax_attention(q.double(), k.double(), v.double(), 0.2, S,
+                                                    sink.double()).reshape(S, H * d)
+    kc, table = _cache_for(S, G, d, torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    t = table[0].cpu()
+    for p in range(S):
+        kc[t[p // 64], :, p % 64] = k[p].cuda()
+        vc[t[p // 64], :, p % 64] = v[p].cuda()
+
+    class KV:
+        pass
+    kv = KV()
+    kv.k, kv.v, kv.table, kv.block_tokens, kv.window = kc, vc, table, 64, 0
+    dev = torch.device("cuda")
+    i32 = dict(dtype=torch.int32, device=dev)
+    fault = torch.zeros(1, **i32)
+    for mode, name in ((1, "prefill_attn_pair"), (2, "prefill_attn_split")):
+        was = ops.set_prefill_pairing(mode)
+        try:
+            for first in (0, 130):
+                T = S - first
+                ctx = StepContext(T=T, B=1, tok_ids=torch.zeros(T, **i32),
+                                  tok_pos=torch.arange(first, S, **i32),
+                                  tok_seq=torch.zeros(T, **i32), seq_slot=torch.zeros(1, **i32),
+                                  seq_start=torch.tensor([first], **i32),
+                                  cu_seqlens=torch.tensor([0, T], **i32), is_decode=False,
+                                  max_new=T, max_context=S, fault=fault, dtype=torch.bfloat16,
+                                  device=dev)
+                before = ops.variant_counts()[name]
+                out = torch.zeros(T, H * d, dtype=torch.bfloat16, device=dev)
+                run_attention(q[first:].reshape(T, H * d).cuda(), out, ctx, kv, H, G, d, 0.2, 0,
+                              torch.bfloat16, sink.cuda())
+                assert ops.variant_counts()[name] == before + 1
+                err = (out.cpu().double() - want[first:]).abs().max()
+                assert err <= 2e-2 * want.abs().max(), (mode, first, float(err))
+        finally:
+            ops.set_prefill_pairing(was)
     assert int(fault.item()) == 0
 
 
