@@ -7,8 +7,8 @@
 // its 32×32 tiled kernel, src/model.cu:141-144, src/kernels/matmul.cu:74-127).
 // cretif_gemm_simt_batched runs `batch` such products in one launch, product z on operands
 // offset by z times an element stride each (per-head matrices on slices of the rows).
-// Any M, N, K; each output sums its products in ascending k whatever M is, so a row's
-// result does not depend on how many other rows are in the call.
+// Any M, N, K; each output sums its products in ascending k, slab of 16 by slab of 16, whatever
+// M is, so a row's result does not depend on how many other rows are in the call.
 #include "api.h"
 #include "common.cuh"
 
@@ -59,6 +59,14 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restr
     }
     __syncthreads();
     if (k0 + BK < K) fetch(k0 + BK);
+    // A slab of 16 products is summed on its own and then added to the running sum: the
+    // running sum takes K / 16 roundings instead of K, which keeps a long row's 32-bit result
+    // within a few units of the last place of the exact one.
+    float part[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) part[i][j] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
       float a[TM], w[TN];
@@ -69,8 +77,12 @@ gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restr
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) part[i][j] = fmaf(a[i], w[j], part[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] += part[i][j];
     __syncthreads();
   }
 #pragma unroll
