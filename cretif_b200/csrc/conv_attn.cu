@@ -23,8 +23,9 @@ namespace {
 constexpr int kCvWarps = 8;
 constexpr int kCvMaxD = 512;
 
-// NCH: channels a lane keeps (head sizes up to 32 NCH)
-template <typename T, int NCH>
+// NCH: channels a lane keeps (head sizes up to 32 NCH).  TAPS: the number of taps when it is 2,
+// 3 or 4 (the loops over them are then unrolled exactly), 0 for any number.
+template <typename T, int NCH, int TAPS>
 __global__ void __launch_bounds__(kCvWarps * 32)
 conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
                                const float* __restrict__ conv_w, int taps,
@@ -36,6 +37,7 @@ conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
                                const int* __restrict__ table, int table_stride,
                                T* __restrict__ kc, T* __restrict__ vc, int bt, int write_cache,
                                unsigned int* __restrict__ fault) {
+  if (TAPS > 0) taps = TAPS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int units = nh + 2 * nkv;
@@ -59,7 +61,7 @@ conv_headnorm_kv_append_kernel(const float* __restrict__ proj, int ldp,
       gain_every > 0 ? 1.0f + gain_coef * logf((float)((pos + 1) / gain_every + 1)) : 1.0f;
   // Where tap j (0 = the oldest) of channel c comes from is the same for every channel: this
   // step's row `back` tokens up, or the sequence's saved inputs; a base and a stride per tap.
-  constexpr int kFastTaps = 8;
+  constexpr int kFastTaps = TAPS > 0 ? TAPS : 8;
   const float* tap_base[kFastTaps];
   int tap_stride[kFastTaps];
 #pragma unroll
@@ -142,11 +144,18 @@ extern "C" int cretif_conv_headnorm_kv_append(
   if (grid.y > 65535) return kBadArgument;
   cudaStream_t st = (cudaStream_t)stream;
   const int widest = nkv > 0 && vd > hd ? vd : hd;
-#define CRETIF_CONV(TT, NCH)                                                                    \
-  conv_headnorm_kv_append_kernel<TT, NCH><<<grid, kCvWarps * 32, 0, st>>>(                       \
+#define CRETIF_CONV_K(TT, NCH, TAPS)                                                            \
+  conv_headnorm_kv_append_kernel<TT, NCH, TAPS><<<grid, kCvWarps * 32, 0, st>>>(                 \
       proj, ldp, conv_w, taps, conv_state, (size_t)state_stride, tok_pos, tok_seq, seq_slot,     \
       seq_start, nh, nkv, hd, vd, eps, gain_coef, gain_every, (TT*)q_out, ldq, table,            \
       table_stride, (TT*)kc, (TT*)vc, bt, write_cache, fault)
+#define CRETIF_CONV(TT, NCH)                                                                    \
+  do {                                                                                          \
+    if (taps == 4) CRETIF_CONV_K(TT, NCH, 4);                                                    \
+    else if (taps == 3) CRETIF_CONV_K(TT, NCH, 3);                                               \
+    else if (taps == 2) CRETIF_CONV_K(TT, NCH, 2);                                               \
+    else CRETIF_CONV_K(TT, NCH, 0);                                                              \
+  } while (0)
 #define CRETIF_CONV_T(TT)                                                                       \
   do {                                                                                          \
     if (widest <= 64) CRETIF_CONV(TT, 2);                                                        \
@@ -162,5 +171,6 @@ extern "C" int cretif_conv_headnorm_kv_append(
     return kBadDType;
 #undef CRETIF_CONV_T
 #undef CRETIF_CONV
+#undef CRETIF_CONV_K
   return launch_status();
 }
